@@ -25,7 +25,7 @@
 // No local memory: the ring takes the whole unified L1, so a stack access is a round trip to L2.  The kernel
 // parameters are __grid_constant__ (never copied to the stack), register buffers are always written in full
 // (a conditionally written element forces the array into local memory), nothing indexes an array at run time.
-// `cuobjdump -res-usage` / tools/sass_histogram.py (profiles/r02_sass_histogram.txt) show what is left.
+// `nvcc -Xptxas -v` shows registers, spills and stack of what is left.
 //
 // Hand-over between phases (KLLM_MEGA_TAGGED=2, default): every produced element is published as
 // one 64-bit {tag, fp32} word and polled in place by the consuming phase -- no fences, flags or

@@ -29,7 +29,6 @@ cap() { # name mode workload steps start
   KLLM_MODE=$2 timeout 300 ncu --set full --clock-control none --import-source on -k regex:decode_megakernel --launch-skip 1 -c 1 -f -o ${O}_mega_$1 \
      python tools/run_decode_once.py --workload $3 --steps $4 --start $5 > ${O}_ncu_$1.log 2>&1; echo "ncu $1 rc=$?"
   python tools/ncu_summarize.py full ${O}_mega_$1.ncu-rep ${O}_megakernel_$1_ncu.txt > /dev/null 2>&1
-  python tools/ncu_hot.py ${O}_mega_$1.ncu-rep 40 > ${O}_megakernel_$1_hot.txt 2>/dev/null
   head -12 ${O}_megakernel_$1_ncu.txt | cut -c1-200
 }
 cap tiny_fast fast tinyllama-1.1b 4 512
