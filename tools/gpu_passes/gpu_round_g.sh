@@ -13,5 +13,5 @@ done
 timeout 600 python bench.py > gpurun_out/g_bench.json 2> gpurun_out/g_bench.err; echo "bench rc=$?"; cat gpurun_out/g_bench.json | cut -c1-400
 timeout 600 ncu --metrics gpu__time_duration.sum --clock-control none -c 400 --csv --log-file gpurun_out/g_launches.csv \
    python bench.py --steps 64 --warmup 3 --no-cpu-baseline > gpurun_out/g_ncu_bench.log 2>&1; echo "ncu launches rc=$?"
-timeout 900 ncu --set full --clock-control none --import-source on -k regex:decode_megakernel -c 1 -f -o gpurun_out/g_mega \
+timeout 900 ncu --set full --clock-control none -k regex:decode_megakernel -c 1 -f -o gpurun_out/g_mega \
    python tools/run_decode_once.py --steps 16 --start 504 > gpurun_out/g_ncu_mega.log 2>&1; echo "ncu mega rc=$?"

@@ -13,7 +13,7 @@ timeout 200 python bench.py --steps 20 --warmup 3 --no-cpu-baseline > ${O}_bench
 timeout 400 python bench.py --workload llama2-7b-int8 --steps 256 --reps 3 --no-cpu-baseline > ${O}_bench_int8.json 2> ${O}_bench_int8.err; echo "bench int8 rc=$?"; cut -c1-400 ${O}_bench_int8.json
 timeout 200 python bench.py --impl reference-cuda --workload tinyllama-1.1b --steps 1024 > ${O}_refcuda_tiny.json 2> ${O}_refcuda_tiny.err; echo "refcuda tiny rc=$?"; cat ${O}_refcuda_tiny.json
 timeout 400 python bench.py --impl reference-cuda --workload llama2-7b-int8 --steps 128 > ${O}_refcuda_int8.json 2> ${O}_refcuda_int8.err; echo "refcuda int8 rc=$?"; cat ${O}_refcuda_int8.json
-timeout 400 ncu --set full --clock-control none --import-source on -k regex:decode_megakernel --launch-skip 1 -c 1 -f -o ${O}_mega_tiny \
+timeout 400 ncu --set full --clock-control none -k regex:decode_megakernel --launch-skip 1 -c 1 -f -o ${O}_mega_tiny \
    python tools/run_decode_once.py --steps 4 --start 256 > ${O}_ncu_tiny.log 2>&1; echo "ncu tiny rc=$?"; tail -2 ${O}_ncu_tiny.log
-timeout 700 ncu --set full --clock-control none --import-source on -k regex:decode_megakernel --launch-skip 1 -c 1 -f -o ${O}_mega_int8 \
+timeout 700 ncu --set full --clock-control none -k regex:decode_megakernel --launch-skip 1 -c 1 -f -o ${O}_mega_int8 \
    python tools/run_decode_once.py --workload llama2-7b-int8 --steps 2 --start 64 > ${O}_ncu_int8.log 2>&1; echo "ncu int8 rc=$?"; tail -2 ${O}_ncu_int8.log

@@ -12,7 +12,7 @@ for wl in stories15m qwen2.5-0.5b; do
   timeout 300 python bench.py --impl reference --workload $wl --steps 32 --warmup 3 > ${O}_bench_reference_arm_${wl}.json 2>> ${O}_bench_reference_arm.err; echo "ref $wl rc=$?"; cut -c1-160 ${O}_bench_reference_arm_${wl}.json
 done
 cap() { # name mode workload steps start
-  KLLM_MODE=$2 timeout 900 ncu --set full --clock-control none --import-source on -k regex:decode_megakernel --launch-skip 1 -c 1 -f -o ${O}_mega_$1 \
+  KLLM_MODE=$2 timeout 900 ncu --set full --clock-control none -k regex:decode_megakernel --launch-skip 1 -c 1 -f -o ${O}_mega_$1 \
      python tools/run_decode_once.py --workload $3 --steps $4 --start $5 > ${O}_ncu_$1.log 2>&1; echo "ncu $1 rc=$?"; tail -1 ${O}_ncu_$1.log | cut -c1-200
 }
 cap tiny_fast fast tinyllama-1.1b 4 512

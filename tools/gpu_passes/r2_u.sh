@@ -25,7 +25,7 @@ run qwen
 BARGS="--workload llama2-7b --steps 128"
 run l7b
 cap() { # name mode workload steps start
-  KLLM_MODE=$2 timeout 300 ncu --set full --clock-control none --import-source on -k regex:decode_megakernel --launch-skip 1 -c 1 -f -o ${O}_mega_$1 \
+  KLLM_MODE=$2 timeout 300 ncu --set full --clock-control none -k regex:decode_megakernel --launch-skip 1 -c 1 -f -o ${O}_mega_$1 \
      python tools/run_decode_once.py --workload $3 --steps $4 --start $5 > ${O}_ncu_$1.log 2>&1; echo "ncu $1 rc=$?"; tail -1 ${O}_ncu_$1.log | cut -c1-160
 }
 cap tiny_fast fast tinyllama-1.1b 4 512

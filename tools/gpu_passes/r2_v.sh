@@ -26,7 +26,7 @@ run qwen
 BARGS="--workload llama2-7b --steps 128"
 run l7b
 cap() { # name mode workload steps start
-  KLLM_MODE=$2 timeout 300 ncu --set full --clock-control none --import-source on -k regex:decode_megakernel --launch-skip 1 -c 1 -f -o ${O}_mega_$1 \
+  KLLM_MODE=$2 timeout 300 ncu --set full --clock-control none -k regex:decode_megakernel --launch-skip 1 -c 1 -f -o ${O}_mega_$1 \
      python tools/run_decode_once.py --workload $3 --steps $4 --start $5 > ${O}_ncu_$1.log 2>&1; echo "ncu $1 rc=$?"
   python tools/ncu_summarize.py full ${O}_mega_$1.ncu-rep ${O}_megakernel_$1_ncu.txt > /dev/null 2>&1
   head -12 ${O}_megakernel_$1_ncu.txt | cut -c1-200

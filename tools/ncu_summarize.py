@@ -48,7 +48,7 @@ def full(src, dst):
     hdr, units = rows[0], rows[1]
     idx = [(k, hdr.index(k)) for k in KEYS if k in hdr]
     with open(dst, "w") as f:
-        f.write(f"# source: {src}  (ncu --set full --clock-control none --import-source on)\n")
+        f.write(f"# source: {src}  (ncu --set full --clock-control none)\n")
         for r in rows[2:]:
             f.write("-" * 100 + "\n")
             for k, i in idx:
