@@ -15,11 +15,6 @@
 
 namespace kllm {
 
-std::atomic<uint64_t>& launch_counter() {
-  static std::atomic<uint64_t> c{0};
-  return c;
-}
-
 // ---- rmsnorm: rmsnorm_kernel.cu:4-50 (one 128-thread block there; one warp carrying the
 // same 128 virtual threads here for the sum, the whole CTA for the scaling pass). ---------
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ x,
@@ -256,22 +251,6 @@ int launch_rope(int flavour, int dim, int kv_dim, int head_size, float* q, float
 using namespace kllm;
 
 extern "C" {
-
-const char* kllm_version(void) { return "kllm_b200 0.1 (sm_100a)"; }
-
-const char* kllm_error_string(int code) {
-  switch (code) {
-    case KLLM_OK: return "ok";
-    case KLLM_E_INVALID: return "invalid argument";
-    case KLLM_E_UNSUPPORTED: return "unsupported shape";
-    case KLLM_E_STATE: return "invalid decoder state";
-    case KLLM_E_NODEVICE: return "no CUDA device";
-    case KLLM_E_COMM: return "tensor-parallel transport unavailable or failed";
-    default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown";
-  }
-}
-
-uint64_t kllm_launch_count(void) { return launch_counter().load(); }
 
 int kllm_rmsnorm_f32(const float* x, const float* w, float* out, int n, float eps, void* stream) {
   if (!x || !w || !out || n <= 0) return KLLM_E_INVALID;

@@ -1,0 +1,470 @@
+// The sequence-batch engine behind include/kllm_seq.h: slot and page management of the key/value pool, and the step
+// function that runs one ragged batch of tokens through the described layer stack.
+//
+// Cache.  One pool of pages per layer run; a page holds `page_tokens` tokens of one sequence ([token][kv_head][dim]
+// keys, [token][kv_head][vdim] values, in the compute type).  All runs share ONE page numbering: a sequence that
+// owns page p owns it in every run's pool, so there is a single page table [slot][i] and a single free list.  A
+// sequence takes pages as it grows (lowest free number first, so freed pages are the next to be used again) and
+// returns them at close.  The table rows of the step's sequences are copied to the device before the kernels run.
+//
+// Step.  Host work: validate, take pages, fill the per-token / per-entry index arrays in pinned memory, one
+// host->device copy.  Device work, per layer run:
+//     resid_norm   (x += run vector)  h = LN_pre(x)
+//     gemm         q | k | v | gate rows in one product
+//     qk_prepare   RMS norms, query temperature, scatter of k / v into the pages, sigmoid of the gates
+//     attention    causal, paged, keys split over CTAs; merge applies the gate
+//     gemm         output projection
+//     resid_norm   x += LN_post(y);  h = LN_pre_ff(x)
+//     router       fp32 logits, softmax, top-k, weights, shared-expert gate
+//     experts      few tokens: pair kernels (weights streamed once per chosen expert)
+//                  many tokens: pairs sorted by expert, two grouped products (SiLU-gate epilogue in the first)
+//     shared       gemm gate|up, silu_mul, gemm down
+//     resid_norm   x += LN_post_ff(routed + g_shared * shared)   [+ the next run's vector and pre-norm, fused]
+// then the final norm on the wanted rows only, the classifier product, argmax, and one device->host copy.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "../../include/kllm_seq.h"
+#include "seq_engine.h"
+
+namespace kllm {
+namespace seq {
+int launch_argmax_rows(const float* logits, int32_t* out, int rows, int vocab, cudaStream_t s);
+}
+}  // namespace kllm
+
+using namespace kllm;
+using namespace kllm::seq;
+
+namespace {
+constexpr int kDefaultPage = 16;
+constexpr int kGroupedMinTokens = 64;  // steps with at least this many tokens run the routed experts as grouped products
+constexpr int kGroupBlock = 64;
+
+inline NormW nw(const kllm_seq_norm& n) { return NormW{n.w, n.b}; }
+inline size_t elt(int dtype) { return dtype == KLLM_SEQ_BF16 ? 2 : 4; }
+
+struct DevBuf {
+  void* p = nullptr;
+  size_t cap = 0;
+  int reserve(size_t bytes) {
+    if (bytes <= cap) return 0;
+    if (p) cudaFree(p);
+    p = nullptr;
+    cap = 0;
+    const size_t want = bytes + bytes / 4 + 256;
+    const cudaError_t e = cudaMalloc(&p, want);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cap = want;
+    return 0;
+  }
+  ~DevBuf() {
+    if (p) cudaFree(p);
+  }
+};
+}  // namespace
+
+struct kllm_seq_engine {
+  kllm_seq_desc d{};
+  std::vector<kllm_seq_layer> layers;
+  std::vector<int32_t> run_layer, run_add;
+  cudaStream_t stream = nullptr;
+  // cache
+  int page = 0, n_pages = 0, table_stride = 0;
+  std::vector<void*> k_pool, v_pool;  // per run
+  int32_t* table_dev = nullptr;       // [max_seqs][table_stride]
+  std::vector<int32_t> table_host;
+  std::vector<int32_t> free_pages;    // kept sorted descending: back() is the lowest number
+  struct Slot {
+    bool live = false;
+    int len = 0;
+    int pages = 0;
+  };
+  std::vector<Slot> slots;
+  // per-step staging
+  int32_t* pinned = nullptr;
+  size_t pinned_cap = 0;
+  DevBuf idx, x, h, proj, q, gates, att, y, y2, ws, top_idx, top_w, sgate, inter, pairs_out, sort, hw, logits, amax;
+  float* logits_pinned = nullptr;
+  size_t logits_pinned_cap = 0;
+  float* trace_host = nullptr;
+  int last_launches = 0;
+  // limits over the layers
+  int max_proj = 0, max_q = 0, max_att = 0, max_heads = 0, max_top = 0, max_ff = 0, max_sff = 0;
+
+  ~kllm_seq_engine() {
+    for (void* p : k_pool) if (p) cudaFree(p);
+    for (void* p : v_pool) if (p) cudaFree(p);
+    if (table_dev) cudaFree(table_dev);
+    if (pinned) cudaFreeHost(pinned);
+    if (logits_pinned) cudaFreeHost(logits_pinned);
+  }
+};
+
+static int validate(const kllm_seq_desc* d) {
+  if (!d || d->width <= 0 || d->vocab <= 0 || d->n_layers <= 0 || !d->layers || d->n_runs <= 0 || !d->run_layer ||
+      !d->embed || !d->head || !d->final_norm.w || d->max_tokens <= 0 || d->max_seqs <= 0)
+    return KLLM_E_INVALID;
+  if (d->dtype != KLLM_SEQ_F32 && d->dtype != KLLM_SEQ_BF16) return KLLM_E_INVALID;
+  for (int r = 0; r < d->n_runs; ++r) {
+    if (d->run_layer[r] < 0 || d->run_layer[r] >= d->n_layers) return KLLM_E_INVALID;
+    if (d->run_add && d->run_add[r] >= 0 && !d->run_vectors) return KLLM_E_INVALID;
+  }
+  for (int i = 0; i < d->n_layers; ++i) {
+    const kllm_seq_layer& L = d->layers[i];
+    if (L.mixer_kind != KLLM_SEQ_MIXER_ATTENTION) return KLLM_E_UNSUPPORTED;
+    const kllm_seq_attention& a = L.attn;
+    if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0 || !a.w_in || !a.w_out ||
+        !L.pre_mixer.w)
+      return KLLM_E_INVALID;
+    if (a.qk_norm && (!a.q_norm_w || !a.k_norm_w)) return KLLM_E_INVALID;
+    if (a.vdim > 256 || a.dim > 512) return KLLM_E_UNSUPPORTED;
+    if (L.ff_kind == KLLM_SEQ_FF_MOE) {
+      const kllm_seq_moe& m = L.moe;
+      if (m.experts <= 0 || m.top <= 0 || m.top > m.experts || m.ff <= 0 || !m.w_router || !m.gate_up || !m.down ||
+          !L.pre_ff.w)
+        return KLLM_E_INVALID;
+      if (m.shared_ff > 0 && (!m.shared_gate_up || !m.shared_down)) return KLLM_E_INVALID;
+    } else if (L.ff_kind != KLLM_SEQ_FF_NONE) {
+      return KLLM_E_UNSUPPORTED;
+    }
+  }
+  return 0;
+}
+
+extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq_engine** out) {
+  if (!out) return KLLM_E_INVALID;
+  *out = nullptr;
+  if (int rc = validate(desc)) return rc;
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) return KLLM_E_NODEVICE;
+  kllm_seq_engine* e = new (std::nothrow) kllm_seq_engine();
+  if (!e) return KLLM_E_STATE;
+  e->d = *desc;
+  e->layers.assign(desc->layers, desc->layers + desc->n_layers);
+  e->run_layer.assign(desc->run_layer, desc->run_layer + desc->n_runs);
+  e->run_add.assign(desc->n_runs, -1);
+  if (desc->run_add) e->run_add.assign(desc->run_add, desc->run_add + desc->n_runs);
+  e->d.layers = e->layers.data();
+  e->d.run_layer = e->run_layer.data();
+  e->d.run_add = e->run_add.data();
+  e->stream = static_cast<cudaStream_t>(stream);
+  e->page = desc->page_tokens > 0 ? desc->page_tokens : kDefaultPage;
+  // every live sequence may leave its last page partly empty
+  e->n_pages = (desc->max_tokens + e->page - 1) / e->page + desc->max_seqs;
+  e->table_stride = (desc->max_tokens + e->page - 1) / e->page + 1;
+  e->slots.resize(desc->max_seqs);
+  e->table_host.assign(static_cast<size_t>(desc->max_seqs) * e->table_stride, 0);
+  for (int p = e->n_pages - 1; p >= 0; --p) e->free_pages.push_back(p);
+  const size_t es = elt(desc->dtype);
+  for (int r = 0; r < desc->n_runs; ++r) {
+    const kllm_seq_attention& a = e->layers[e->run_layer[r]].attn;
+    void *k = nullptr, *v = nullptr;
+    const size_t rows = static_cast<size_t>(e->n_pages) * e->page * a.kv_heads;
+    if (cudaMalloc(&k, rows * a.dim * es) != cudaSuccess || cudaMalloc(&v, rows * a.vdim * es) != cudaSuccess) {
+      if (k) cudaFree(k);
+      delete e;
+      return static_cast<int>(cudaErrorMemoryAllocation);
+    }
+    e->k_pool.push_back(k);
+    e->v_pool.push_back(v);
+  }
+  if (cudaMalloc(&e->table_dev, e->table_host.size() * sizeof(int32_t)) != cudaSuccess) {
+    delete e;
+    return static_cast<int>(cudaErrorMemoryAllocation);
+  }
+  cudaMemset(e->table_dev, 0, e->table_host.size() * sizeof(int32_t));
+  for (const kllm_seq_layer& L : e->layers) {
+    const kllm_seq_attention& a = L.attn;
+    e->max_proj = std::max(e->max_proj, a.heads * a.dim + a.kv_heads * (a.dim + a.vdim) + (a.gate ? a.heads : 0));
+    e->max_q = std::max(e->max_q, a.heads * a.dim);
+    e->max_att = std::max(e->max_att, a.heads * a.vdim);
+    e->max_heads = std::max(e->max_heads, a.heads);
+    if (L.ff_kind == KLLM_SEQ_FF_MOE) {
+      e->max_top = std::max(e->max_top, L.moe.top);
+      e->max_ff = std::max(e->max_ff, L.moe.top * L.moe.ff);
+      e->max_sff = std::max(e->max_sff, L.moe.shared_ff);
+    }
+  }
+  *out = e;
+  return 0;
+}
+
+extern "C" void kllm_seq_destroy(kllm_seq_engine* eng) {
+  if (!eng) return;
+  cudaStreamSynchronize(eng->stream);
+  delete eng;
+}
+
+extern "C" int kllm_seq_open(kllm_seq_engine* e, int32_t* seq_out) {
+  if (!e || !seq_out) return KLLM_E_INVALID;
+  for (size_t i = 0; i < e->slots.size(); ++i)
+    if (!e->slots[i].live) {
+      e->slots[i] = kllm_seq_engine::Slot{true, 0, 0};
+      *seq_out = static_cast<int32_t>(i);
+      return 0;
+    }
+  return KLLM_E_STATE;
+}
+
+extern "C" int kllm_seq_close(kllm_seq_engine* e, int32_t seq) {
+  if (!e || seq < 0 || seq >= static_cast<int32_t>(e->slots.size()) || !e->slots[seq].live) return KLLM_E_INVALID;
+  kllm_seq_engine::Slot& s = e->slots[seq];
+  for (int i = 0; i < s.pages; ++i) e->free_pages.push_back(e->table_host[static_cast<size_t>(seq) * e->table_stride + i]);
+  std::sort(e->free_pages.begin(), e->free_pages.end(), [](int a, int b) { return a > b; });
+  s = kllm_seq_engine::Slot{};
+  return 0;
+}
+
+extern "C" int kllm_seq_length(const kllm_seq_engine* e, int32_t seq) {
+  if (!e || seq < 0 || seq >= static_cast<int32_t>(e->slots.size()) || !e->slots[seq].live) return KLLM_E_INVALID;
+  return e->slots[seq].len;
+}
+
+extern "C" int kllm_seq_free_pages(const kllm_seq_engine* e) {
+  return e ? static_cast<int>(e->free_pages.size()) : KLLM_E_INVALID;
+}
+
+extern "C" int kllm_seq_trace_residual(kllm_seq_engine* e, float* residual_host) {
+  if (!e) return KLLM_E_INVALID;
+  e->trace_host = residual_host;
+  return 0;
+}
+
+extern "C" int kllm_seq_last_launches(const kllm_seq_engine* e) { return e ? e->last_launches : KLLM_E_INVALID; }
+
+#define RC(call)                  \
+  do {                            \
+    const int rc_ = (call);       \
+    if (rc_ != 0) return rc_;     \
+  } while (0)
+#define CU(call)                                          \
+  do {                                                    \
+    const cudaError_t ce_ = (call);                       \
+    if (ce_ != cudaSuccess) return static_cast<int>(ce_); \
+  } while (0)
+
+extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_t* seqs, const int32_t* counts,
+                             const int32_t* tokens_host, int32_t n_want, const int32_t* want_host, float* logits_host,
+                             int32_t* argmax_host) {
+  if (!e || n_entries <= 0 || !seqs || !counts || !tokens_host || n_want < 0 || (n_want > 0 && !want_host))
+    return KLLM_E_INVALID;
+  const kllm_seq_desc& d = e->d;
+  const int W = d.width, dtype = d.dtype;
+  const size_t es = elt(dtype);
+  cudaStream_t st = e->stream;
+  const uint64_t launches_before = launch_counter().load();
+
+  // ---- host: validate, pages, index arrays ------------------------------------------------------------------------
+  int T = 0, max_count = 0, max_ctx = 0, need_pages = 0;
+  for (int i = 0; i < n_entries; ++i) {
+    const int s = seqs[i];
+    if (s < 0 || s >= static_cast<int>(e->slots.size()) || !e->slots[s].live || counts[i] <= 0) return KLLM_E_INVALID;
+    for (int j = 0; j < i; ++j)
+      if (seqs[j] == s) return KLLM_E_INVALID;  // one entry per sequence and step
+    const int new_len = e->slots[s].len + counts[i];
+    need_pages += (new_len + e->page - 1) / e->page - e->slots[s].pages;
+    T += counts[i];
+    max_count = std::max(max_count, counts[i]);
+    max_ctx = std::max(max_ctx, new_len);
+  }
+  int live_tokens = 0;
+  for (const auto& s : e->slots) live_tokens += s.live ? s.len : 0;
+  if (live_tokens + T > d.max_tokens || need_pages > static_cast<int>(e->free_pages.size())) return KLLM_E_STATE;
+  for (int i = 0; i < T; ++i)
+    if (tokens_host[i] < 0 || tokens_host[i] >= d.vocab) return KLLM_E_INVALID;
+  for (int i = 0; i < n_want; ++i)
+    if (want_host[i] < 0 || want_host[i] >= T) return KLLM_E_INVALID;
+
+  // layout of the index block (int32): tokens[T] tok_seq[T] tok_pos[T] ent_first[E] ent_count[E] ent_seq[E] ent_pos0[E]
+  // want[n_want]
+  const size_t n_idx = 3 * static_cast<size_t>(T) + 4 * static_cast<size_t>(n_entries) + static_cast<size_t>(n_want);
+  if (n_idx > e->pinned_cap) {
+    if (e->pinned) cudaFreeHost(e->pinned);
+    e->pinned = nullptr;
+    e->pinned_cap = 0;
+    CU(cudaMallocHost(&e->pinned, (n_idx + n_idx / 2) * sizeof(int32_t)));
+    e->pinned_cap = n_idx + n_idx / 2;
+  }
+  RC(e->idx.reserve(n_idx * sizeof(int32_t)));
+  int32_t* hp = e->pinned;
+  int32_t *h_tok = hp, *h_seq = hp + T, *h_pos = hp + 2 * T, *h_first = hp + 3 * T, *h_count = h_first + n_entries,
+          *h_eseq = h_count + n_entries, *h_pos0 = h_eseq + n_entries, *h_want = h_pos0 + n_entries;
+  std::memcpy(h_tok, tokens_host, static_cast<size_t>(T) * sizeof(int32_t));
+  int at = 0;
+  for (int i = 0; i < n_entries; ++i) {
+    kllm_seq_engine::Slot& s = e->slots[seqs[i]];
+    h_first[i] = at, h_count[i] = counts[i], h_eseq[i] = seqs[i], h_pos0[i] = s.len;
+    for (int j = 0; j < counts[i]; ++j) h_seq[at + j] = seqs[i], h_pos[at + j] = s.len + j;
+    at += counts[i];
+    const int new_len = s.len + counts[i];
+    const int pages = (new_len + e->page - 1) / e->page;
+    int32_t* row = e->table_host.data() + static_cast<size_t>(seqs[i]) * e->table_stride;
+    if (pages > e->table_stride) return KLLM_E_STATE;
+    while (s.pages < pages) {
+      row[s.pages++] = e->free_pages.back();
+      e->free_pages.pop_back();
+    }
+    s.len = new_len;
+    CU(cudaMemcpyAsync(e->table_dev + static_cast<size_t>(seqs[i]) * e->table_stride, row, pages * sizeof(int32_t),
+                       cudaMemcpyHostToDevice, st));
+  }
+  if (n_want) std::memcpy(h_want, want_host, static_cast<size_t>(n_want) * sizeof(int32_t));
+  // the table rows above are pageable host memory: the copies are staged by the driver before the call returns
+  CU(cudaMemcpyAsync(e->idx.p, hp, n_idx * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  const int32_t* d_tok = static_cast<const int32_t*>(e->idx.p);
+  const int32_t *d_seq = d_tok + T, *d_pos = d_tok + 2 * T, *d_first = d_tok + 3 * T, *d_count = d_first + n_entries,
+                *d_eseq = d_count + n_entries, *d_pos0 = d_eseq + n_entries, *d_want = d_pos0 + n_entries;
+
+  // ---- workspaces ----------------------------------------------------------------------------------------------
+  // keys of a row tile are split over CTAs when the step itself offers few tiles (decode, short prompts)
+  int splits = 1;
+  {
+    const int tiles = (max_ctx + kAttnKeys - 1) / kAttnKeys;
+    const int ctas = n_entries * ((max_count * 8 + kAttnRows - 1) / kAttnRows);
+    if (ctas < 64) splits = std::max(1, std::min({tiles, 32, 128 / std::max(1, ctas)}));
+  }
+  const size_t Ts = static_cast<size_t>(T);
+  RC(e->x.reserve(Ts * W * 4));
+  RC(e->h.reserve(Ts * W * es));
+  RC(e->proj.reserve(Ts * std::max({e->max_proj, 2 * e->max_sff, W}) * 4));
+  RC(e->q.reserve(Ts * e->max_q * es));
+  RC(e->gates.reserve(Ts * e->max_heads * 4));
+  RC(e->att.reserve(Ts * std::max(e->max_att, e->max_sff) * es));
+  RC(e->y.reserve(Ts * W * 4));
+  RC(e->y2.reserve(Ts * W * 4));
+  size_t ws_bytes = 0;
+  for (const kllm_seq_layer& L : e->layers) {
+    AttnShape a{L.attn.heads, L.attn.kv_heads, L.attn.dim, L.attn.vdim, 0, 0, 0, 0, 0};
+    ws_bytes = std::max(ws_bytes, attention_workspace_bytes(a, T, splits));
+  }
+  RC(e->ws.reserve(ws_bytes));
+  const bool grouped = T >= kGroupedMinTokens;
+  if (e->max_top > 0) {
+    RC(e->top_idx.reserve(Ts * e->max_top * 4));
+    RC(e->top_w.reserve(Ts * e->max_top * 4));
+    RC(e->sgate.reserve(Ts * 4));
+    RC(e->inter.reserve(Ts * e->max_ff * es));
+    if (grouped) RC(e->pairs_out.reserve(Ts * e->max_top * W * 4));
+  }
+  float* x = static_cast<float*>(e->x.p);
+  float* proj = static_cast<float*>(e->proj.p);
+  float* y = static_cast<float*>(e->y.p);
+  float* y2 = static_cast<float*>(e->y2.p);
+  const bool tracing = e->trace_host != nullptr;
+
+  // ---- device: the layer runs -------------------------------------------------------------------------------------
+  RC(launch_embed(dtype, d.embed, d_tok, x, T, W, st));
+  bool pre_done = false;  // the previous run's last kernel already produced this run's h (and added its vector)
+  for (int r = 0; r < d.n_runs; ++r) {
+    const kllm_seq_layer& L = e->layers[e->run_layer[r]];
+    const kllm_seq_attention& A = L.attn;
+    const AttnShape shape{A.heads, A.kv_heads, A.dim, A.vdim, A.scale, A.temp_coef, A.temp_every, A.qk_norm, A.gate};
+    const PagedKV kv{e->k_pool[r], e->v_pool[r], e->table_dev, e->table_stride, e->page};
+    if (!pre_done) {
+      ResidNormArgs a{};
+      a.x = x, a.add = e->run_add[r] >= 0 ? d.run_vectors + static_cast<size_t>(e->run_add[r]) * W : nullptr;
+      a.pre = nw(L.pre_mixer), a.out = e->h.p, a.T = T, a.width = W, a.dtype = dtype, a.eps = d.norm_eps;
+      RC(launch_resid_norm(a, st));
+    }
+    pre_done = false;
+    const int n_proj = A.heads * A.dim + A.kv_heads * (A.dim + A.vdim) + (A.gate ? A.heads : 0);
+    RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, n_proj, st));
+    RC(launch_qk_prepare(dtype, shape, proj, A.q_norm_w, A.k_norm_w, d.norm_eps, d_seq, d_pos, e->q.p,
+                         static_cast<float*>(e->gates.p), kv, T, st));
+    RC(launch_attention(dtype, shape, e->q.p, static_cast<const float*>(e->gates.p), kv, n_entries, d_first, d_count,
+                        d_eseq, d_pos0, max_count, max_ctx, splits, static_cast<float*>(e->ws.p), e->att.p, T, d_seq,
+                        d_pos, st));
+    RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
+
+    // what follows this layer run: the next run's vector and pre-norm can ride on this run's last kernel
+    const bool last = r + 1 == d.n_runs;
+    const float* next_add = nullptr;
+    NormW next_pre{nullptr, nullptr};
+    if (!last && !tracing) {
+      next_add = e->run_add[r + 1] >= 0 ? d.run_vectors + static_cast<size_t>(e->run_add[r + 1]) * W : nullptr;
+      next_pre = nw(e->layers[e->run_layer[r + 1]].pre_mixer);
+    }
+    if (L.ff_kind == KLLM_SEQ_FF_NONE) {
+      ResidNormArgs a{};
+      a.x = x, a.y1 = y, a.post = nw(L.post_mixer), a.T = T, a.width = W, a.dtype = dtype, a.eps = d.norm_eps;
+      if (next_pre.w) a.add = next_add, a.pre = next_pre, a.out = e->h.p, pre_done = true;
+      RC(launch_resid_norm(a, st));
+    } else {
+      const kllm_seq_moe& M = L.moe;
+      {
+        ResidNormArgs a{};
+        a.x = x, a.y1 = y, a.post = nw(L.post_mixer), a.pre = nw(L.pre_ff), a.out = e->h.p, a.T = T, a.width = W;
+        a.dtype = dtype, a.eps = d.norm_eps;
+        RC(launch_resid_norm(a, st));
+      }
+      int32_t* top_idx = static_cast<int32_t*>(e->top_idx.p);
+      float* top_w = static_cast<float*>(e->top_w.p);
+      float* sgate = static_cast<float*>(e->sgate.p);
+      RC(launch_router(dtype, e->h.p, M.w_router, M.shared_ff > 0 ? M.w_shared_gate : nullptr, M.experts, M.top,
+                       M.router_scale, top_idx, top_w, sgate, T, W, st));
+      if (!grouped) {
+        RC(launch_expert_gate_up(dtype, e->h.p, M.gate_up, top_idx, e->inter.p, T, M.top, M.ff, W, st));
+        RC(launch_expert_down(dtype, e->inter.p, M.down, top_idx, top_w, y, T, M.top, M.ff, W, st));
+      } else {
+        const int n_pairs = T * M.top;
+        const int cap = ((n_pairs + kGroupBlock - 1) / kGroupBlock + M.experts) * kGroupBlock;
+        const int n_blocks = cap / kGroupBlock;
+        RC(e->sort.reserve((static_cast<size_t>(M.experts) + 1 + cap + n_blocks) * 4));
+        int32_t* counts_d = static_cast<int32_t*>(e->sort.p);
+        int32_t* sorted = counts_d + M.experts + 1;
+        int32_t* block_expert = sorted + cap;
+        RC(launch_sort_pairs(top_idx, n_pairs, M.experts, kGroupBlock, counts_d, sorted, block_expert, cap, st));
+        GroupedArgs g{};
+        g.a = e->h.p, g.w = M.gate_up, g.sorted_pair = sorted, g.block_expert = block_expert, g.a_row_div = M.top;
+        g.n_blocks = n_blocks, g.block = kGroupBlock, g.K = W, g.N = M.ff, g.epilogue = 1, g.out = e->inter.p;
+        RC(gemm_grouped(dtype, g, st));
+        g.a = e->inter.p, g.w = M.down, g.a_row_div = 1, g.K = M.ff, g.N = W, g.epilogue = 0, g.out = e->pairs_out.p;
+        RC(gemm_grouped(dtype, g, st));
+        RC(launch_combine_pairs(static_cast<const float*>(e->pairs_out.p), top_w, y, T, M.top, W, st));
+      }
+      const bool shared = M.shared_ff > 0;
+      if (shared) {
+        RC(gemm(dtype, e->h.p, M.shared_gate_up, proj, T, W, 2 * M.shared_ff, st));
+        RC(launch_silu_mul(dtype, proj, e->att.p, T, M.shared_ff, st));
+        RC(gemm(dtype, e->att.p, M.shared_down, y2, T, M.shared_ff, W, st));
+      }
+      ResidNormArgs a{};
+      a.x = x, a.y1 = y, a.y2 = shared ? y2 : nullptr, a.s2 = shared && M.w_shared_gate ? sgate : nullptr;
+      a.post = nw(L.post_ff), a.T = T, a.width = W, a.dtype = dtype, a.eps = d.norm_eps;
+      if (next_pre.w) a.add = next_add, a.pre = next_pre, a.out = e->h.p, pre_done = true;
+      RC(launch_resid_norm(a, st));
+    }
+    if (tracing)
+      CU(cudaMemcpyAsync(e->trace_host + static_cast<size_t>(r) * T * W, x, Ts * W * 4, cudaMemcpyDeviceToHost, st));
+  }
+  e->trace_host = nullptr;
+
+  // ---- the wanted rows: final norm, classifier, greedy id -------------------------------------------------------
+  if (n_want > 0) {
+    RC(e->hw.reserve(static_cast<size_t>(n_want) * W * es));
+    RC(e->logits.reserve(static_cast<size_t>(n_want) * d.vocab * 4));
+    RC(e->amax.reserve(static_cast<size_t>(n_want) * 4));
+    ResidNormArgs a{};
+    a.x = x, a.pre = nw(d.final_norm), a.out = e->hw.p, a.rows = d_want, a.T = n_want, a.width = W, a.dtype = dtype;
+    a.eps = d.norm_eps;
+    RC(launch_resid_norm(a, st));
+    float* lg = static_cast<float*>(e->logits.p);
+    RC(gemm(dtype, e->hw.p, d.head, lg, n_want, W, d.vocab, st));
+    if (argmax_host) {
+      RC(launch_argmax_rows(lg, static_cast<int32_t*>(e->amax.p), n_want, d.vocab, st));
+      CU(cudaMemcpyAsync(argmax_host, e->amax.p, static_cast<size_t>(n_want) * 4, cudaMemcpyDeviceToHost, st));
+    }
+    if (logits_host)
+      CU(cudaMemcpyAsync(logits_host, lg, static_cast<size_t>(n_want) * d.vocab * 4, cudaMemcpyDeviceToHost, st));
+  }
+  e->last_launches = static_cast<int>(launch_counter().load() - launches_before);
+  CU(cudaStreamSynchronize(st));
+  return 0;
+}

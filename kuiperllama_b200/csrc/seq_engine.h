@@ -1,0 +1,131 @@
+// Internal interface between the translation units of the sequence-batch engine (seq_engine.cu: the
+// step function, the paged cache and its slot manager; seq_kernels.cu: norms, query/key preparation,
+// paged attention, router and expert kernels; seq_gemm.cu: token-block matrix products).
+//
+// Conventions.  A step processes T tokens of several sequences as ONE ragged batch: activations are
+// [T, .] row-major with no padding, and three int32 arrays describe the rows -- tok_seq[t] (cache slot of
+// the row's sequence), tok_pos[t] (its position, counted from 0 in the sequence) and, per entry of the
+// step, ent_first[e] / ent_count[e] / ent_seq[e] / ent_pos0[e].  The residual stream, every norm, every
+// softmax and the router are fp32 whatever the compute type; `AT` below is the activation / weight type
+// of the matrix products (float, or __nv_bfloat16 with fp32 accumulation).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../../include/kllm_seq.h"
+#include "kllm_host.h"
+
+namespace kllm {
+namespace seq {
+
+constexpr int kAttnRows = 32;   // (token, query head) rows of one attention CTA
+constexpr int kAttnKeys = 64;   // keys per tile
+constexpr int kAttnThreads = 128;
+
+struct NormW {
+  const float* w;
+  const float* b;  // may be null: no bias
+};
+
+// Where the keys and values of one layer run live: pages of `page` tokens, [n_pages][page][kv_heads][dim].
+struct PagedKV {
+  void* k;
+  void* v;
+  const int32_t* table;  // [slots][table_stride]: page number of the i-th page of a sequence
+  int table_stride;
+  int page;
+};
+
+struct AttnShape {
+  int heads, kv_heads, dim, vdim;
+  float scale;
+  float temp_coef;  // query temperature 1 + coef * ln(floor((p + 1) / every) + 1); every == 0: none
+  int temp_every;
+  int qk_norm;      // RMS norm of each query / key head with a shared weight vector
+  int gate;         // one sigmoid gate per (token, head) on the attention output
+};
+
+// ---- seq_kernels.cu -----------------------------------------------------------------------------------------------
+int launch_embed(int dtype, const void* table, const int32_t* tokens, float* x, int T, int width, cudaStream_t s);
+
+// x += LN(y1 + s2[t] * y2; post) (optional; y2 optional);  x += add (a [width] vector, optional);
+// out = LN(x; pre) in the compute type (optional) -- in this order.  `rows` (optional) gathers: row i reads x[rows[i]], and x is then
+// left untouched (only `out` is written).
+struct ResidNormArgs {
+  float* x;
+  const float* add;
+  const float* y1;
+  const float* y2;
+  const float* s2;
+  NormW post;
+  NormW pre;
+  void* out;
+  const int32_t* rows;
+  int T, width, dtype;
+  float eps;
+};
+int launch_resid_norm(const ResidNormArgs& a, cudaStream_t s);
+
+// qkvg: [T, heads*dim + kv_heads*dim + kv_heads*vdim + (gate ? heads : 0)] fp32 (projection output).
+// Writes q [T, heads, dim] (compute type; normed, temperature applied), the key / value rows into the pages, and the
+// gates sigmoid(.) [T, heads] fp32.
+int launch_qk_prepare(int dtype, const AttnShape& a, const float* qkvg, const float* qnorm_w, const float* knorm_w,
+                      float eps, const int32_t* tok_seq, const int32_t* tok_pos, void* q, float* gates,
+                      const PagedKV& kv, int T, cudaStream_t s);
+
+// Causal softmax attention of the step's rows over their sequences' pages.  out [T, heads*vdim] (compute type).
+// `splits` CTAs share the keys of a row tile; partial (max, sum, unnormalised output) go through `ws`.
+size_t attention_workspace_bytes(const AttnShape& a, int T, int splits);
+int launch_attention(int dtype, const AttnShape& a, const void* q, const float* gates, const PagedKV& kv,
+                     int n_entries, const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
+                     const int32_t* ent_pos0, int max_count, int max_ctx, int splits, float* ws, void* out, int T,
+                     const int32_t* tok_seq, const int32_t* tok_pos, cudaStream_t s);
+
+// Router: z = Wr h (fp32), s = softmax(z), the `top` largest, weights s / (sum + 1e-20) * scale; shared-expert gate
+// sigmoid(w_sg . h) when w_sg is given.
+int launch_router(int dtype, const void* h, const float* w_router, const float* w_sg, int experts, int top,
+                  float scale, int32_t* top_idx, float* top_w, float* sgate, int T, int width, cudaStream_t s);
+
+// Routed experts, one (token, chosen expert) pair at a time: inter[pair] = silu(Wg h) * (Wu h), then
+// y[t] = sum_k w_k * Wd_k inter[t, k].  gate_up: [experts][2*ff][width] (gate rows, then up rows); down:
+// [experts][width][ff].
+int launch_expert_gate_up(int dtype, const void* h, const void* gate_up, const int32_t* top_idx, void* inter, int T,
+                          int top, int ff, int width, cudaStream_t s);
+int launch_expert_down(int dtype, const void* inter, const void* down, const int32_t* top_idx, const float* top_w,
+                       float* y, int T, int top, int ff, int width, cudaStream_t s);
+
+// y[t] = sum_k w[t, k] * yp[t * top + k]   (fp32 [T * top, width] -> [T, width])
+int launch_combine_pairs(const float* yp, const float* top_w, float* y, int T, int top, int width, cudaStream_t s);
+
+// out[t, f] = silu(gu[t, f]) * gu[t, ff + f]   (gu fp32 [T, 2*ff], out compute type [T, ff])
+int launch_silu_mul(int dtype, const float* gu, void* out, int T, int ff, cudaStream_t s);
+
+// Routed experts over token blocks (prefill): rows grouped by expert.  sort_pairs builds, on the device, the list of
+// pairs ordered by expert in blocks of `block` rows (padded with -1), and the expert of every block.
+int launch_sort_pairs(const int32_t* top_idx, int n_pairs, int experts, int block, int32_t* counts /*[experts+1]*/,
+                      int32_t* sorted_pair /*[cap]*/, int32_t* block_expert /*[cap/block]*/, int cap, cudaStream_t s);
+
+// ---- seq_gemm.cu --------------------------------------------------------------------------------------------------
+// out[T, N] (fp32) = a[T, K] . w[N, K]^T, a and w in the compute type, fp32 accumulation.
+int gemm(int dtype, const void* a, const void* w, float* out, int T, int K, int N, cudaStream_t s);
+// Grouped form for the routed experts: block b (of `block` rows) multiplies rows a[row_of(b, i)] with the weights of
+// expert block_expert[b]; see seq_gemm.cu.
+struct GroupedArgs {
+  const void* a;            // [*, K]
+  const void* w;            // [experts][N][K]
+  const int32_t* sorted_pair;   // [n_blocks * block] pair index or -1
+  const int32_t* block_expert;  // [n_blocks] expert or -1
+  int a_row_div;            // row of `a` for pair p is p / a_row_div (gate_up: top; down: 1)
+  int n_blocks, block, K, N;
+  // epilogue: 0 = out[pair, n] = acc (fp32);  1 = out[pair, f] = silu(acc_gate) * acc_up in the compute type (the
+  // weights hold ff gate rows, then ff up rows; N = ff)
+  int epilogue;
+  void* out;
+};
+int gemm_grouped(int dtype, const GroupedArgs& g, cudaStream_t s);
+
+inline int cuda_rc(cudaError_t e) { return static_cast<int>(e); }
+}  // namespace seq
+}  // namespace kllm

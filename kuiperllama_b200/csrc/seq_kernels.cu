@@ -1,0 +1,760 @@
+// Kernels of the sequence-batch engine other than the matrix products: embedding rows, the fused residual /
+// layer-norm step, query-key preparation with the scatter into the paged cache, causal paged attention (prompt tiles
+// and single decode rows through the same kernel, keys split over CTAs), the softmax router with top-k selection, and
+// the routed experts one (token, expert) pair at a time for steps of a few tokens.
+//
+// Every kernel is a template on the compute type AT (float or __nv_bfloat16): what the matrix products read and
+// write.  Norms, scores, softmax weights, router and residual are fp32 in both instantiations.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cfloat>
+#include <cstdint>
+
+#include "seq_engine.h"
+
+namespace kllm {
+namespace seq {
+namespace {
+
+constexpr unsigned kAll = 0xffffffffu;
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename AT> __device__ __forceinline__ AT from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kAll, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(kAll, v, o));
+  return v;
+}
+// sum over the block; `red` holds one float per warp (+1).  Every thread gets the total.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // `red` may still be read from the previous reduction
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+// 16-byte vectors of the compute type, widened to fp32
+template <typename AT> struct VecOf;
+template <> struct VecOf<float> {
+  static constexpr int N = 4;
+  __device__ static __forceinline__ void load(const float* p, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
+  }
+};
+template <> struct VecOf<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(u[i] << 16);
+      f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+  }
+};
+
+// dot of a weight row (compute type, global) with an fp32 vector in shared memory, spread over the warp's lanes;
+// every lane returns the total.
+template <typename AT>
+__device__ __forceinline__ float warp_dot(const AT* __restrict__ w, const float* __restrict__ xs, int K, int lane) {
+  constexpr int V = VecOf<AT>::N;
+  float acc = 0.f;
+  if ((K % V) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    for (int k = lane * V; k < K; k += 32 * V) {
+      float f[V];
+      VecOf<AT>::load(w + k, f);
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc = fmaf(f[i], xs[k + i], acc);
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) acc = fmaf(to_f(w[k]), xs[k], acc);
+  }
+  return warp_sum(acc);
+}
+
+// ---- embedding ----------------------------------------------------------------------------------------------------
+template <typename AT>
+__global__ void embed_kernel(const AT* __restrict__ table, const int32_t* __restrict__ tokens, float* __restrict__ x,
+                             int width) {
+  const int t = blockIdx.x;
+  const AT* row = table + static_cast<size_t>(tokens[t]) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) x[static_cast<size_t>(t) * width + i] = to_f(row[i]);
+}
+
+// ---- residual + layer norms ---------------------------------------------------------------------------------------
+// Layer norm as the model family defines it: (v - mean) / sqrt(var + eps) * w + b, var = mean of squared deviations.
+template <typename AT>
+__global__ void resid_norm_kernel(ResidNormArgs a) {
+  extern __shared__ float buf[];  // [width]
+  __shared__ float red[33];
+  const int W = a.width;
+  const int r = blockIdx.x;
+  const size_t src = static_cast<size_t>(a.rows ? a.rows[r] : r) * W;
+  const size_t dst = static_cast<size_t>(r) * W;
+  const float inv_w = 1.0f / static_cast<float>(W);
+  const bool has_post = a.post.w != nullptr;
+  if (has_post) {
+    float s = 0.f;
+    const float g = a.s2 ? a.s2[r] : 1.0f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      float u = a.y1 ? a.y1[src + i] : 0.f;
+      if (a.y2) u += g * a.y2[src + i];
+      buf[i] = u;
+      s += u;
+    }
+    const float mean = block_sum(s, red) * inv_w;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float d = buf[i] - mean;
+      q += d * d;
+    }
+    const float var = block_sum(q, red) * inv_w;
+    const float rstd = 1.0f / sqrtf(var + a.eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      float v = a.x[src + i];
+      v += (buf[i] - mean) * rstd * a.post.w[i] + (a.post.b ? a.post.b[i] : 0.f);
+      if (a.add) v += a.add[i];
+      buf[i] = v;
+      if (!a.rows) a.x[dst + i] = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      float v = a.x[src + i];
+      if (a.add) {
+        v += a.add[i];
+        if (!a.rows) a.x[dst + i] = v;
+      }
+      buf[i] = v;
+    }
+  }
+  if (a.pre.w == nullptr) return;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += buf[i];
+  const float mean = block_sum(s, red) * inv_w;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float d = buf[i] - mean;
+    q += d * d;
+  }
+  const float var = block_sum(q, red) * inv_w;
+  const float rstd = 1.0f / sqrtf(var + a.eps);
+  AT* out = static_cast<AT*>(a.out) + dst;
+  for (int i = threadIdx.x; i < W; i += blockDim.x)
+    out[i] = from_f<AT>((buf[i] - mean) * rstd * a.pre.w[i] + (a.pre.b ? a.pre.b[i] : 0.f));
+}
+
+// ---- query / key preparation ----------------------------------------------------------------------------------------
+template <typename AT>
+__device__ __forceinline__ AT* page_row(AT* base, const PagedKV& kv, int seq, int pos, int heads, int dim) {
+  const int page = kv.table[static_cast<size_t>(seq) * kv.table_stride + pos / kv.page];
+  return base + (static_cast<size_t>(page) * kv.page + pos % kv.page) * heads * dim;
+}
+
+template <typename AT>
+__global__ void qk_prepare_kernel(AttnShape a, const float* __restrict__ qkvg, const float* __restrict__ qnorm_w,
+                                  const float* __restrict__ knorm_w, float eps, const int32_t* __restrict__ tok_seq,
+                                  const int32_t* __restrict__ tok_pos, AT* __restrict__ q, float* __restrict__ gates,
+                                  PagedKV kv) {
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int qn = a.heads * a.dim, kn = a.kv_heads * a.dim, vn = a.kv_heads * a.vdim;
+  const int stride = qn + kn + vn + (a.gate ? a.heads : 0);
+  const float* row = qkvg + static_cast<size_t>(t) * stride;
+  const int seq = tok_seq[t], pos = tok_pos[t];
+  float temp = 1.0f;
+  if (a.temp_every > 0) temp = 1.0f + a.temp_coef * logf(static_cast<float>((pos + 1) / a.temp_every) + 1.0f);
+  AT* krow = page_row(static_cast<AT*>(kv.k), kv, seq, pos, a.kv_heads, a.dim);
+  AT* vrow = page_row(static_cast<AT*>(kv.v), kv, seq, pos, a.kv_heads, a.vdim);
+  for (int u = warp; u < a.heads + a.kv_heads; u += nw) {
+    const bool is_q = u < a.heads;
+    const float* src = row + (is_q ? u * a.dim : qn + (u - a.heads) * a.dim);
+    AT* dst = is_q ? q + (static_cast<size_t>(t) * a.heads + u) * a.dim : krow + (u - a.heads) * a.dim;
+    float rinv = 1.0f;
+    if (a.qk_norm) {
+      float ss = 0.f;
+      for (int d = lane; d < a.dim; d += 32) ss += src[d] * src[d];
+      ss = warp_sum(ss);
+      rinv = 1.0f / sqrtf(ss / static_cast<float>(a.dim) + eps);
+    }
+    const float* nw_ = is_q ? qnorm_w : knorm_w;
+    for (int d = lane; d < a.dim; d += 32) {
+      float v = src[d];
+      if (a.qk_norm) v = v * rinv * nw_[d];
+      if (is_q) v *= temp;
+      dst[d] = from_f<AT>(v);
+    }
+  }
+  for (int i = threadIdx.x; i < vn; i += blockDim.x) vrow[i] = from_f<AT>(row[qn + kn + i]);
+  if (a.gate)
+    for (int h = threadIdx.x; h < a.heads; h += blockDim.x)
+      gates[static_cast<size_t>(t) * a.heads + h] = 1.0f / (1.0f + expf(-row[qn + kn + vn + h]));
+}
+
+// ---- attention ------------------------------------------------------------------------------------------------------
+// One CTA: one entry of the step, one key/value head g, kAttnRows consecutive rows (row r of the entry = token r / rep,
+// query head g * rep + r % rep, rep = heads / kv_heads), one split of the keys.  Tiles of kAttnKeys keys go through
+// shared memory in fp32; scores, the running maximum / sum and the output accumulators are fp32 (online softmax).
+// The partial result of a split is (m, l, o[vdim]) per row; attention_merge_kernel combines the splits, applies the
+// output gate and converts to the compute type.
+template <typename AT, int C>
+__global__ void __launch_bounds__(kAttnThreads)
+attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_t* __restrict__ ent_first,
+                 const int32_t* __restrict__ ent_count, const int32_t* __restrict__ ent_seq,
+                 const int32_t* __restrict__ ent_pos0, int splits, float* __restrict__ ws) {
+  const int e = blockIdx.y / a.kv_heads, g = blockIdx.y % a.kv_heads, split = blockIdx.z;
+  const int rep = a.heads / a.kv_heads;
+  const int count = ent_count[e], first = ent_first[e], seq = ent_seq[e], pos0 = ent_pos0[e];
+  const int n_rows = count * rep;
+  const int r0 = blockIdx.x * kAttnRows;
+  if (r0 >= n_rows) return;
+  const int rows_here = min(kAttnRows, n_rows - r0);
+  const int pmax = pos0 + (r0 + rows_here - 1) / rep;  // last position any row of the tile sees
+  const int n_tiles = pmax / kAttnKeys + 1;
+  const int per = (n_tiles + splits - 1) / splits;
+  const int tile_lo = split * per, tile_hi = min(n_tiles, tile_lo + per);
+
+  const int dq = (a.dim + 3) & ~3, dk = dq + 1;
+  extern __shared__ float sm[];
+  float* Qs = sm;                                  // [rows][dq], scaled
+  float* Ks = Qs + kAttnRows * dq;                 // [keys][dk]
+  float* Vs = Ks + kAttnKeys * dk;                 // [keys][vdim]
+  float* Ss = Vs + kAttnKeys * a.vdim;             // [rows][keys]
+  float* m_s = Ss + kAttnRows * kAttnKeys;         // [rows]
+  float* l_s = m_s + kAttnRows;
+  float* al_s = l_s + kAttnRows;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < kAttnRows * dq; i += kAttnThreads) {
+    const int r = i / dq, d = i % dq;
+    float v = 0.f;
+    if (r < rows_here && d < a.dim) {
+      const int rr = r0 + r;
+      const int t = first + rr / rep, h = g * rep + rr % rep;
+      v = to_f(q[(static_cast<size_t>(t) * a.heads + h) * a.dim + d]) * a.scale;
+    }
+    Qs[i] = v;
+  }
+  if (tid < kAttnRows) {
+    m_s[tid] = -INFINITY;
+    l_s[tid] = 0.f;
+  }
+  // this thread's part of the score tile and of the output
+  const int key = tid % kAttnKeys, rg = tid / kAttnKeys;  // rows rg*16 .. rg*16+15
+  constexpr int RPT = kAttnRows / (kAttnThreads / kAttnKeys);  // 16
+  float acc[RPT][C];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i)
+#pragma unroll
+    for (int c = 0; c < C; ++c) acc[i][c] = 0.f;
+
+  const AT* kbase = static_cast<const AT*>(kv.k);
+  const AT* vbase = static_cast<const AT*>(kv.v);
+  const int32_t* table = kv.table + static_cast<size_t>(seq) * kv.table_stride;
+
+  for (int tile = tile_lo; tile < tile_hi; ++tile) {
+    const int k0 = tile * kAttnKeys;
+    __syncthreads();  // previous tile's K, V, S are no longer read
+    for (int j = warp; j < kAttnKeys; j += kAttnThreads / 32) {
+      const int kj = k0 + j;
+      float* kd = Ks + j * dk;
+      float* vd = Vs + j * a.vdim;
+      if (kj <= pmax) {
+        const size_t slot = static_cast<size_t>(table[kj / kv.page]) * kv.page + kj % kv.page;
+        const AT* ksrc = kbase + (slot * a.kv_heads + g) * a.dim;
+        const AT* vsrc = vbase + (slot * a.kv_heads + g) * a.vdim;
+        for (int d = lane; d < dk; d += 32) kd[d] = d < a.dim ? to_f(ksrc[d]) : 0.f;
+        for (int d = lane; d < a.vdim; d += 32) vd[d] = to_f(vsrc[d]);
+      } else {
+        for (int d = lane; d < dk; d += 32) kd[d] = 0.f;
+        for (int d = lane; d < a.vdim; d += 32) vd[d] = 0.f;
+      }
+    }
+    __syncthreads();
+    {  // scores
+      float sc[RPT];
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) sc[i] = 0.f;
+      const float* kp = Ks + key * dk;
+      for (int d = 0; d < dq; d += 4) {
+        const float k0v = kp[d], k1v = kp[d + 1], k2v = kp[d + 2], k3v = kp[d + 3];
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+          const float4 qv = *reinterpret_cast<const float4*>(Qs + (rg * RPT + i) * dq + d);
+          sc[i] = fmaf(qv.x, k0v, sc[i]);
+          sc[i] = fmaf(qv.y, k1v, sc[i]);
+          sc[i] = fmaf(qv.z, k2v, sc[i]);
+          sc[i] = fmaf(qv.w, k3v, sc[i]);
+        }
+      }
+      const int kj = k0 + key;
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        const int r = rg * RPT + i;
+        const bool visible = r < rows_here && kj <= pos0 + (r0 + r) / rep;
+        Ss[r * kAttnKeys + key] = visible ? sc[i] : -INFINITY;
+      }
+    }
+    __syncthreads();
+    for (int r = warp; r < kAttnRows; r += kAttnThreads / 32) {  // online softmax, a warp per row
+      const float v0 = Ss[r * kAttnKeys + lane], v1 = Ss[r * kAttnKeys + lane + 32];
+      const float m_old = m_s[r];
+      const float m_new = fmaxf(m_old, warp_max(fmaxf(v0, v1)));
+      float p0 = 0.f, p1 = 0.f, alpha = 1.0f;
+      if (m_new > -INFINITY) {
+        p0 = expf(v0 - m_new);
+        p1 = expf(v1 - m_new);
+        alpha = expf(m_old - m_new);
+      }
+      Ss[r * kAttnKeys + lane] = p0;
+      Ss[r * kAttnKeys + lane + 32] = p1;
+      const float s = warp_sum(p0 + p1);
+      if (lane == 0) {
+        m_s[r] = m_new;
+        l_s[r] = l_s[r] * alpha + s;
+        al_s[r] = alpha;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const float al = al_s[rg * RPT + i];
+#pragma unroll
+      for (int c = 0; c < C; ++c) acc[i][c] *= al;
+    }
+    for (int j = 0; j < kAttnKeys; j += 4) {
+      float vv[4][C];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          const int col = key + c * kAttnKeys;
+          vv[jj][c] = col < a.vdim ? Vs[(j + jj) * a.vdim + col] : 0.f;
+        }
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        const float4 p = *reinterpret_cast<const float4*>(Ss + (rg * RPT + i) * kAttnKeys + j);
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          acc[i][c] = fmaf(p.x, vv[0][c], acc[i][c]);
+          acc[i][c] = fmaf(p.y, vv[1][c], acc[i][c]);
+          acc[i][c] = fmaf(p.z, vv[2][c], acc[i][c]);
+          acc[i][c] = fmaf(p.w, vv[3][c], acc[i][c]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int pstride = a.vdim + 2;
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int r = rg * RPT + i;
+    if (r >= rows_here) continue;
+    const int rr = r0 + r;
+    const int t = first + rr / rep, h = g * rep + rr % rep;
+    float* p = ws + ((static_cast<size_t>(t) * a.heads + h) * splits + split) * pstride;
+    if (key == 0) {
+      p[0] = m_s[r];
+      p[1] = l_s[r];
+    }
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      const int col = key + c * kAttnKeys;
+      if (col < a.vdim) p[2 + col] = acc[i][c];
+    }
+  }
+}
+
+template <typename AT>
+__global__ void attention_merge_kernel(int heads, int vdim, int splits, const float* __restrict__ ws,
+                                       const float* __restrict__ gates, AT* __restrict__ out) {
+  const size_t th = blockIdx.x;  // t * heads + h
+  const int pstride = vdim + 2;
+  const float* p = ws + th * splits * pstride;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, p[s * pstride]);
+  float L = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float m = p[s * pstride];
+    if (m > -INFINITY) L += p[s * pstride + 1] * expf(m - M);
+  }
+  const float gate = gates ? gates[th] : 1.0f;
+  for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float m = p[s * pstride];
+      if (m > -INFINITY) o += p[s * pstride + 2 + d] * expf(m - M);
+    }
+    out[th * vdim + d] = from_f<AT>(o / L * gate);
+  }
+}
+
+// ---- router ---------------------------------------------------------------------------------------------------------
+template <typename AT>
+__global__ void router_kernel(const AT* __restrict__ h, const float* __restrict__ w_router,
+                              const float* __restrict__ w_sg, int experts, int top, float scale,
+                              int32_t* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ sgate, int T,
+                              int width) {
+  extern __shared__ float sm[];  // [warps][experts]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int t = blockIdx.x * nw + warp;
+  if (t >= T) return;
+  float* z = sm + warp * experts;
+  const AT* x = h + static_cast<size_t>(t) * width;
+  for (int e = 0; e < experts; ++e) {
+    const float* w = w_router + static_cast<size_t>(e) * width;
+    float acc = 0.f;
+    for (int k = lane; k < width; k += 32) acc = fmaf(w[k], to_f(x[k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc;
+  }
+  if (w_sg) {
+    float acc = 0.f;
+    for (int k = lane; k < width; k += 32) acc = fmaf(w_sg[k], to_f(x[k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) sgate[t] = 1.0f / (1.0f + expf(-acc));
+  }
+  __syncwarp();
+  float mx = -INFINITY;
+  for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < experts; e += 32) {
+    const float p = expf(z[e] - mx);
+    z[e] = p;
+    sum += p;
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < experts; e += 32) z[e] = z[e] / sum;
+  __syncwarp();
+  float chosen_sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -1.0f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = z[e];
+      if (v > best) best = v, bi = e;  // ascending e: the lowest index wins a tie inside the lane
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(kAll, best, o);
+      const int oi = __shfl_xor_sync(kAll, bi, o);
+      if (ob > best || (ob == best && oi < bi)) best = ob, bi = oi;
+    }
+    chosen_sum += best;
+    if (lane == 0) {
+      top_idx[static_cast<size_t>(t) * top + k] = bi;
+      top_w[static_cast<size_t>(t) * top + k] = best;
+      z[bi] = -2.0f;  // softmax outputs are >= 0: never chosen again
+    }
+    __syncwarp();
+  }
+  const float inv = scale / (chosen_sum + 1e-20f);
+  if (lane < top) top_w[static_cast<size_t>(t) * top + lane] *= inv;
+  for (int k = lane + 32; k < top; k += 32) top_w[static_cast<size_t>(t) * top + k] *= inv;
+}
+
+// ---- routed experts, pair by pair ----------------------------------------------------------------------------------
+constexpr int kPairRows = 16;  // expert rows per CTA
+template <typename AT>
+__global__ void expert_gate_up_kernel(const AT* __restrict__ h, const AT* __restrict__ gate_up,
+                                      const int32_t* __restrict__ top_idx, AT* __restrict__ inter, int top, int ff,
+                                      int width) {
+  extern __shared__ float xs[];  // [width]
+  const int pair = blockIdx.x, t = pair / top, e = top_idx[pair];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(h[static_cast<size_t>(t) * width + i]);
+  __syncthreads();
+  const AT* wg = gate_up + static_cast<size_t>(e) * 2 * ff * width;
+  const AT* wu = wg + static_cast<size_t>(ff) * width;
+  const int f_end = min(ff, (blockIdx.y + 1) * kPairRows);
+  for (int f = blockIdx.y * kPairRows + warp; f < f_end; f += nw) {
+    const float gv = warp_dot(wg + static_cast<size_t>(f) * width, xs, width, lane);
+    const float uv = warp_dot(wu + static_cast<size_t>(f) * width, xs, width, lane);
+    if (lane == 0) inter[static_cast<size_t>(pair) * ff + f] = from_f<AT>(gv / (1.0f + expf(-gv)) * uv);
+  }
+}
+
+template <typename AT>
+__global__ void expert_down_kernel(const AT* __restrict__ inter, const AT* __restrict__ down,
+                                   const int32_t* __restrict__ top_idx, const float* __restrict__ top_w,
+                                   float* __restrict__ y, int top, int ff, int width) {
+  extern __shared__ float xs[];  // [top][ff]
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) xs[i] = to_f(inter[static_cast<size_t>(t) * top * ff + i]);
+  __syncthreads();
+  const int n_end = min(width, (blockIdx.y + 1) * kPairRows);
+  for (int n = blockIdx.y * kPairRows + warp; n < n_end; n += nw) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int e = top_idx[static_cast<size_t>(t) * top + k];
+      const AT* w = down + (static_cast<size_t>(e) * width + n) * ff;
+      acc += top_w[static_cast<size_t>(t) * top + k] * warp_dot(w, xs + k * ff, ff, lane);
+    }
+    if (lane == 0) y[static_cast<size_t>(t) * width + n] = acc;
+  }
+}
+
+__global__ void combine_pairs_kernel(const float* __restrict__ yp, const float* __restrict__ top_w,
+                                     float* __restrict__ y, int top, int width) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k)
+      acc += top_w[static_cast<size_t>(t) * top + k] * yp[(static_cast<size_t>(t) * top + k) * width + i];
+    y[static_cast<size_t>(t) * width + i] = acc;
+  }
+}
+
+template <typename AT>
+__global__ void silu_mul_kernel(const float* __restrict__ gu, AT* __restrict__ out, int ff, size_t total) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t t = i / ff;
+  const int f = static_cast<int>(i % ff);
+  const float g = gu[t * 2 * ff + f], u = gu[t * 2 * ff + ff + f];
+  out[i] = from_f<AT>(g / (1.0f + expf(-g)) * u);
+}
+
+// ---- greedy id of each logits row (lowest index on ties) ------------------------------------------------------------
+__global__ void argmax_rows_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int vocab) {
+  __shared__ float bv[32];
+  __shared__ int bi[32];
+  const float* row = logits + static_cast<size_t>(blockIdx.x) * vocab;
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best || (v == best && i < idx)) best = v, idx = i;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(kAll, best, o);
+    const int oi = __shfl_xor_sync(kAll, idx, o);
+    if (ob > best || (ob == best && oi < idx)) best = ob, idx = oi;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) bv[warp] = best, bi[warp] = idx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w)
+      if (bv[w] > best || (bv[w] == best && bi[w] < idx)) best = bv[w], idx = bi[w];
+    out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+  }
+}
+
+// ---- pairs grouped by expert (one CTA; the lists are short) --------------------------------------------------------
+__global__ void sort_pairs_kernel(const int32_t* __restrict__ top_idx, int n_pairs, int experts, int block,
+                                  int32_t* __restrict__ counts, int32_t* __restrict__ sorted_pair,
+                                  int32_t* __restrict__ block_expert, int cap) {
+  extern __shared__ int32_t sh[];  // [experts] counts, [experts + 1] block offsets
+  int32_t* cnt = sh;
+  int32_t* off = sh + experts;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&cnt[top_idx[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0;
+    for (int e = 0; e < experts; ++e) {
+      off[e] = o;
+      counts[e] = cnt[e];
+      o += (cnt[e] + block - 1) / block * block;
+    }
+    off[experts] = o;
+    counts[experts] = o;
+  }
+  __syncthreads();
+  const int used = off[experts];
+  for (int i = threadIdx.x; i < cap; i += blockDim.x) sorted_pair[i] = -1;
+  for (int b = threadIdx.x; b < cap / block; b += blockDim.x) {
+    int ex = -1;
+    if (b * block < used)
+      for (int e = 0; e < experts; ++e)
+        if (b * block >= off[e] && b * block < off[e + 1]) ex = e;
+    block_expert[b] = ex;
+  }
+  __syncthreads();
+  // stable fill: each expert's pairs in ascending pair order (one thread per expert walks the list)
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    int o = off[e];
+    if (cnt[e] == 0) continue;
+    for (int p = 0; p < n_pairs; ++p)
+      if (top_idx[p] == e) sorted_pair[o++] = p;
+  }
+}
+
+#define KLLM_SEQ_DISPATCH(dtype, CALL)                         \
+  do {                                                         \
+    if ((dtype) == KLLM_SEQ_F32) {                             \
+      using AT = float;                                        \
+      CALL;                                                    \
+    } else if ((dtype) == KLLM_SEQ_BF16) {                     \
+      using AT = __nv_bfloat16;                                \
+      CALL;                                                    \
+    } else {                                                   \
+      return KLLM_E_INVALID;                                   \
+    }                                                          \
+  } while (0)
+
+inline int done() {
+  count_launch();
+  return cuda_rc(cudaGetLastError());
+}
+
+}  // namespace
+
+int launch_embed(int dtype, const void* table, const int32_t* tokens, float* x, int T, int width, cudaStream_t s) {
+  KLLM_SEQ_DISPATCH(dtype, (embed_kernel<AT><<<T, 128, 0, s>>>(static_cast<const AT*>(table), tokens, x, width)));
+  return done();
+}
+
+int launch_resid_norm(const ResidNormArgs& a, cudaStream_t s) {
+  const size_t smem = static_cast<size_t>(a.width) * sizeof(float);
+  if (smem > 200 * 1024) return KLLM_E_UNSUPPORTED;
+  const int threads = a.width >= 1024 ? 256 : 128;
+  if (smem > 48 * 1024) {
+    KLLM_SEQ_DISPATCH(a.dtype, (cudaFuncSetAttribute(resid_norm_kernel<AT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     static_cast<int>(smem))));
+  }
+  KLLM_SEQ_DISPATCH(a.dtype, (resid_norm_kernel<AT><<<a.T, threads, smem, s>>>(a)));
+  return done();
+}
+
+int launch_qk_prepare(int dtype, const AttnShape& a, const float* qkvg, const float* qnorm_w, const float* knorm_w,
+                      float eps, const int32_t* tok_seq, const int32_t* tok_pos, void* q, float* gates,
+                      const PagedKV& kv, int T, cudaStream_t s) {
+  KLLM_SEQ_DISPATCH(dtype, (qk_prepare_kernel<AT><<<T, 128, 0, s>>>(a, qkvg, qnorm_w, knorm_w, eps, tok_seq, tok_pos,
+                                                                    static_cast<AT*>(q), gates, kv)));
+  return done();
+}
+
+size_t attention_workspace_bytes(const AttnShape& a, int T, int splits) {
+  return static_cast<size_t>(T) * a.heads * splits * (a.vdim + 2) * sizeof(float);
+}
+
+template <typename AT, int C>
+static int launch_attention_c(const AttnShape& a, const void* q, const PagedKV& kv, int n_entries,
+                              const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
+                              const int32_t* ent_pos0, int max_count, int splits, float* ws, cudaStream_t s) {
+  const int dq = (a.dim + 3) & ~3;
+  const size_t smem = (static_cast<size_t>(kAttnRows) * dq + static_cast<size_t>(kAttnKeys) * (dq + 1) +
+                       static_cast<size_t>(kAttnKeys) * a.vdim + kAttnRows * kAttnKeys + 3 * kAttnRows) * sizeof(float);
+  if (smem > 220 * 1024) return KLLM_E_UNSUPPORTED;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    const cudaError_t e = cudaFuncSetAttribute(attention_kernel<AT, C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(smem));
+    if (e != cudaSuccess) return cuda_rc(e);
+    configured = smem;
+  }
+  const int rep = a.heads / a.kv_heads;
+  const dim3 grid((max_count * rep + kAttnRows - 1) / kAttnRows, n_entries * a.kv_heads, splits);
+  attention_kernel<AT, C><<<grid, kAttnThreads, smem, s>>>(a, static_cast<const AT*>(q), kv, ent_first, ent_count,
+                                                          ent_seq, ent_pos0, splits, ws);
+  return done();
+}
+
+int launch_attention(int dtype, const AttnShape& a, const void* q, const float* gates, const PagedKV& kv,
+                     int n_entries, const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
+                     const int32_t* ent_pos0, int max_count, int max_ctx, int splits, float* ws, void* out, int T,
+                     const int32_t* tok_seq, const int32_t* tok_pos, cudaStream_t s) {
+  (void)max_ctx, (void)tok_seq, (void)tok_pos;
+  if (a.kv_heads <= 0 || a.heads % a.kv_heads != 0 || a.vdim > 4 * kAttnKeys || a.dim <= 0 || a.vdim <= 0)
+    return KLLM_E_UNSUPPORTED;
+  const int C = (a.vdim + kAttnKeys - 1) / kAttnKeys;
+  int rc = 0;
+#define KLLM_ATTN_C(c)                                                                                              \
+  KLLM_SEQ_DISPATCH(dtype, (rc = launch_attention_c<AT, c>(a, q, kv, n_entries, ent_first, ent_count, ent_seq, ent_pos0, \
+                                                           max_count, splits, ws, s)))
+  switch (C) {
+    case 1: KLLM_ATTN_C(1); break;
+    case 2: KLLM_ATTN_C(2); break;
+    case 3: KLLM_ATTN_C(3); break;
+    default: KLLM_ATTN_C(4); break;
+  }
+#undef KLLM_ATTN_C
+  if (rc) return rc;
+  KLLM_SEQ_DISPATCH(dtype, (attention_merge_kernel<AT><<<T * a.heads, 64, 0, s>>>(a.heads, a.vdim, splits, ws,
+                                                                                 a.gate ? gates : nullptr,
+                                                                                 static_cast<AT*>(out))));
+  return done();
+}
+
+int launch_router(int dtype, const void* h, const float* w_router, const float* w_sg, int experts, int top,
+                  float scale, int32_t* top_idx, float* top_w, float* sgate, int T, int width, cudaStream_t s) {
+  if (top > experts || experts <= 0 || top <= 0) return KLLM_E_INVALID;
+  const int warps = 4;
+  const size_t smem = static_cast<size_t>(warps) * experts * sizeof(float);
+  if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
+  KLLM_SEQ_DISPATCH(dtype, (router_kernel<AT><<<(T + warps - 1) / warps, warps * 32, smem, s>>>(
+                               static_cast<const AT*>(h), w_router, w_sg, experts, top, scale, top_idx, top_w, sgate, T,
+                               width)));
+  return done();
+}
+
+int launch_expert_gate_up(int dtype, const void* h, const void* gate_up, const int32_t* top_idx, void* inter, int T,
+                          int top, int ff, int width, cudaStream_t s) {
+  const size_t smem = static_cast<size_t>(width) * sizeof(float);
+  if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
+  const dim3 grid(T * top, (ff + kPairRows - 1) / kPairRows);
+  KLLM_SEQ_DISPATCH(dtype, (expert_gate_up_kernel<AT><<<grid, 128, smem, s>>>(static_cast<const AT*>(h),
+                                                                             static_cast<const AT*>(gate_up), top_idx,
+                                                                             static_cast<AT*>(inter), top, ff, width)));
+  return done();
+}
+
+int launch_expert_down(int dtype, const void* inter, const void* down, const int32_t* top_idx, const float* top_w,
+                       float* y, int T, int top, int ff, int width, cudaStream_t s) {
+  const size_t smem = static_cast<size_t>(top) * ff * sizeof(float);
+  if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
+  const dim3 grid(T, (width + kPairRows - 1) / kPairRows);
+  KLLM_SEQ_DISPATCH(dtype, (expert_down_kernel<AT><<<grid, 128, smem, s>>>(static_cast<const AT*>(inter),
+                                                                          static_cast<const AT*>(down), top_idx, top_w,
+                                                                          y, top, ff, width)));
+  return done();
+}
+
+int launch_combine_pairs(const float* yp, const float* top_w, float* y, int T, int top, int width, cudaStream_t s) {
+  combine_pairs_kernel<<<T, 256, 0, s>>>(yp, top_w, y, top, width);
+  return done();
+}
+
+int launch_silu_mul(int dtype, const float* gu, void* out, int T, int ff, cudaStream_t s) {
+  const size_t total = static_cast<size_t>(T) * ff;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  KLLM_SEQ_DISPATCH(dtype, (silu_mul_kernel<AT><<<blocks, 256, 0, s>>>(gu, static_cast<AT*>(out), ff, total)));
+  return done();
+}
+
+int launch_argmax_rows(const float* logits, int32_t* out, int rows, int vocab, cudaStream_t s) {
+  argmax_rows_kernel<<<rows, 256, 0, s>>>(logits, out, vocab);
+  return done();
+}
+
+int launch_sort_pairs(const int32_t* top_idx, int n_pairs, int experts, int block, int32_t* counts,
+                      int32_t* sorted_pair, int32_t* block_expert, int cap, cudaStream_t s) {
+  const size_t smem = (2 * static_cast<size_t>(experts) + 1) * sizeof(int32_t);
+  if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
+  sort_pairs_kernel<<<1, 1024, smem, s>>>(top_idx, n_pairs, experts, block, counts, sorted_pair, block_expert, cap);
+  return done();
+}
+
+}  // namespace seq
+}  // namespace kllm
