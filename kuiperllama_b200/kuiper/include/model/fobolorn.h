@@ -22,6 +22,7 @@ namespace model {
 class FobolornModel final : public SequenceModel {
  protected:
   base::Status build(const json::Value& config, const SafetensorsFile& weights) override;
+  base::Status check_folder(const json::Value& config, const SafetensorsFile& weights) override;
 
  private:
   base::Status build_attention(const json::Value& mixer, const SafetensorsFile& w, const std::string& prefix,

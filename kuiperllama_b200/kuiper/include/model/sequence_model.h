@@ -66,6 +66,11 @@ class SequenceModel : public base::NoCopyable {
  protected:
   // the model family: read its configuration, pack its weights (upload_*), fill layers_ / run_* / embed_ ...
   virtual base::Status build(const json::Value& config, const SafetensorsFile& weights) = 0;
+  // what can be said about the folder without a device (used to report a bad folder on a machine without a GPU)
+  virtual base::Status check_folder(const json::Value& config, const SafetensorsFile& weights) {
+    (void)config, (void)weights;
+    return base::error::Success();
+  }
 
   // ---- helpers for build() ----
   // `parts` stacked along the first axis into one device tensor of the compute type (rows of all parts must have

@@ -85,6 +85,30 @@ base::Status FobolornModel::build_moe(const json::Value& c, const SafetensorsFil
   return base::error::Success();
 }
 
+// every tensor the configuration implies, by name
+base::Status FobolornModel::check_folder(const json::Value& config, const SafetensorsFile& w) {
+  base::Status st;
+  for (const char* name : {"embed", "head", "final.norm", "final.norm.b"}) need(w, name, &st);
+  const auto& layers = config.at("layers").array;
+  for (size_t i = 0; i < layers.size(); ++i) {
+    const std::string p = "l" + std::to_string(i) + ".";
+    if (layers[i].at("type").as_string() != "attention")
+      return base::error::FunctionNotImplement("layer " + std::to_string(i) + ": unknown mixer");
+    std::vector<std::string> names = {"norm1", "norm1.b", "norm1b", "norm1b.b", "mix.q", "mix.k", "mix.v", "mix.g", "mix.o",
+                                      "mix.q.norm", "mix.k.norm"};
+    if (layers[i].has("mlp")) {
+      const json::Value& mc = layers[i].at("mlp");
+      for (const char* n : {"norm2", "norm2.b", "norm2b", "norm2b.b", "mlp.router"}) names.push_back(n);
+      for (int e = 0; e < get_int(mc.at("router"), "experts"); ++e)
+        for (const char* n : {"gate", "up", "down"}) names.push_back("mlp.e" + std::to_string(e) + "." + n);
+      if (mc.has("shared"))
+        for (const char* n : {"gate", "up", "down", "sg"}) names.push_back(std::string("mlp.shared.") + n);
+    }
+    for (const std::string& n : names) need(w, p + n, &st);
+  }
+  return st;
+}
+
 base::Status FobolornModel::build(const json::Value& config, const SafetensorsFile& w) {
   vocab_ = get_int(config, "vocab");
   width_ = get_int(config, "width");

@@ -91,8 +91,14 @@ base::Status SequenceModel::init(const std::string& dir, const SequenceOptions& 
   ss << in.rdbuf();
   SafetensorsFile weights;
   if (base::Status st = weights.open(dir + "/model.safetensors"); !st) return st;
+  int devices = 0;
+  const bool have_device = cudaGetDeviceCount(&devices) == cudaSuccess && devices > 0;
   try {
     const json::Value config = json::parse(ss.str());
+    if (!have_device) {  // no CPU fallback: say so, after the checks of the folder that need no device
+      if (base::Status st = check_folder(config, weights); !st) return st;
+      return base::error::InternalError("no CUDA device: batched models run on the GPU only");
+    }
     if (base::Status st = build(config, weights); !st) return st;
   } catch (const std::exception& e) {
     return base::error::ModelParseError(dir + "/config.json: " + e.what());

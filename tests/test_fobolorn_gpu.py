@@ -1,0 +1,232 @@
+"""Fobolorn through the product path (bin/trace_run -> registry -> BatchScheduler -> sequence-batch engine and its
+kernels) against the plain float64 restatement in tests/fobolorn_oracle.py.  Small random models, bf16-representable
+weights; --dtype float32 is compared tightly, bfloat16 loosely."""
+import numpy as np
+import pytest
+import torch
+
+from fobolorn_oracle import forward, greedy, make_config, make_weights, write_model
+from seq_util import ROOT, rel_err, run_trace, whole
+
+pytestmark = pytest.mark.gpu
+TOL32 = 1e-4   # fp32 kernels against float64: rounding only (peaky softmax amplifies it; a lost key costs > 1e-2)
+TOL16 = 4e-2   # bf16 products
+
+
+def toks(n, vocab, seed):
+    return [int(t) for t in np.random.default_rng(seed).integers(0, vocab, n)]
+
+
+def ref_logits(cfg, w, tokens):
+    return forward(cfg, w, tokens).numpy()
+
+
+@pytest.fixture(scope="module")
+def base(tmp_path_factory):
+    """Two different layers, a loop over one of them, odd sizes (dim not a multiple of 4, a value size between one
+    and two key tiles of columns), a temperature step every 5 positions."""
+    cfg = make_config(width=72, vocab=101, layers=3, heads=6, kv_heads=2, dim=18, vdim=40, experts=5, top=2, ff=24,
+                      shared_ff=40, loop=(1, 3, 2), q_temp=(0.7, 5))
+    cfg["layers"][2]["mixer"].update(heads=3, kv_heads=3, dim=32, vdim=72)          # no grouping, wide values
+    cfg["layers"][1]["mlp"]["router"].update(experts=3, top=3)                       # every expert chosen
+    w = make_weights(cfg, seed=1, sharp=4.0)
+    d = write_model(tmp_path_factory.mktemp("fobo_base"), cfg, w)
+    return cfg, w, d
+
+
+# ---- every mechanism on its own -------------------------------------------------------------------------------------
+def one_layer(tmp_path, **kw):
+    cfg = make_config(layers=1, **kw)
+    w = make_weights(cfg, seed=3, sharp=3.0)
+    return cfg, w, write_model(tmp_path, cfg, w)
+
+
+@pytest.mark.parametrize("case", ["attention_only", "no_temperature", "no_shared", "experts_only", "top1", "mha",
+                                  "one_kv_head", "scale_const"])
+def test_mechanism_alone(tmp_path, case):
+    kw = dict(width=48, vocab=50, heads=4, kv_heads=2, dim=12, vdim=20, experts=4, top=2, ff=16, shared_ff=24)
+    if case == "attention_only":
+        kw.update(mlp=False)
+    elif case == "no_temperature":
+        kw.update(q_temp=None)
+    elif case == "no_shared":
+        kw.update(shared_ff=0)
+    elif case == "top1":
+        kw.update(top=1, router_scale=0.75)
+    elif case == "mha":
+        kw.update(kv_heads=4)
+    elif case == "one_kv_head":
+        kw.update(kv_heads=1)
+    elif case == "scale_const":
+        kw.update(scale=0.31)
+    cfg, w, d = one_layer(tmp_path, **kw)
+    if case == "experts_only":  # the mixer's output projection is zero: what is left of the layer is the feed-forward
+        w["l0.mix.o"] = torch.zeros_like(w["l0.mix.o"])
+        write_model(d, cfg, w)
+    t = toks(37, cfg["vocab"], 5)
+    resid_ref = []
+    ref = forward(cfg, w, t, resid_ref).numpy()
+    logits, resid = run_trace(d, [whole("a", t)], residual=True)
+    got_resid = resid[0].reshape(1, len(t), cfg["width"])
+    assert np.abs(got_resid[0] - resid_ref[0].numpy()).max() < 2e-4
+    assert rel_err(logits[0], ref) < TOL32
+
+
+def test_residual_after_every_layer_run(base):
+    cfg, w, d = base
+    t = toks(29, cfg["vocab"], 7)
+    resid_ref = []
+    forward(cfg, w, t, resid_ref)
+    _, resid = run_trace(d, [whole("a", t)], residual=True)
+    got = resid[0].reshape(len(resid_ref), len(t), cfg["width"])
+    assert len(resid_ref) == 1 + 2 * 2  # layer 0, then layers 1..2 twice
+    for r, ref in enumerate(resid_ref):
+        assert np.abs(got[r] - ref.numpy()).max() < 1e-4 * max(1.0, float(ref.abs().max())), f"layer run {r}"
+
+
+# ---- whole prompts, far keys, page and tile borders -----------------------------------------------------------------
+@pytest.mark.parametrize("page", [4, 16, 64])
+def test_long_prompt_every_position(base, page):
+    cfg, w, d = base
+    t = toks(203, cfg["vocab"], 11)  # past three key tiles of 64, not a multiple of any page size
+    ref = ref_logits(cfg, w, t)
+    logits, _ = run_trace(d, [whole("a", t)], page=page)
+    err = [rel_err(logits[0][i:i + 1], ref[i:i + 1]) for i in range(len(t))]
+    assert max(err) < TOL32, f"first bad position {int(np.argmax(np.array(err) >= TOL32))}"
+
+
+def test_one_far_key_carries_the_output(tmp_path):
+    """Every query is made to look at position 3 only (one key scaled up, peaky softmax): a cache that loses or
+    misplaces that key changes every later logit."""
+    cfg = make_config(width=32, vocab=40, layers=1, heads=2, kv_heads=1, dim=8, vdim=16, mlp=False, q_temp=None, scale=4.0)
+    w = make_weights(cfg, seed=9)
+    special = 7
+    t = toks(150, cfg["vocab"], 13)
+    t = [x if x != special else special + 1 for x in t]
+    t[3] = special
+    # keys are unit-normed, so make the special token's key point along the mean query direction by weights alone:
+    # the key projection reads only the special token's embedding direction strongly
+    w["embed"][special] = 6.0 * torch.sign(w["embed"][special])
+    ref = ref_logits(cfg, w, t)
+    d = write_model(tmp_path, cfg, w)
+    steps = [whole("a", t[:100], end=False)] + [{"entries": [{"id": "a", "tokens": [x], "want": [0]}]} for x in t[100:]]
+    logits, _ = run_trace(d, steps, page=16)
+    got = np.concatenate([logits[0]] + logits[1:])
+    assert rel_err(got, ref) < TOL32
+
+
+# ---- prompt against token-by-token decoding, long decoding ----------------------------------------------------------
+def test_prefill_equals_stepwise_decoding(base):
+    cfg, w, d = base
+    t = toks(90, cfg["vocab"], 17)
+    ref = ref_logits(cfg, w, t)
+    one_by_one = [{"entries": [{"id": "s", "tokens": [x], "want": [0]}]} for x in t]     # from the very first token
+    split = [whole("p", t[:2], end=False)] + [{"entries": [{"id": "p", "tokens": [x], "want": [0]}]} for x in t[2:]]
+    logits, _ = run_trace(d, one_by_one + split, page=8)
+    a = np.concatenate(logits[:len(t)])
+    b = np.concatenate(logits[len(t):])
+    assert rel_err(a, ref) < TOL32 and rel_err(b, ref) < TOL32
+    assert rel_err(a, b) < TOL32
+
+
+def test_long_decoding_crosses_tiles_and_temperature_steps(base):
+    cfg, w, d = base
+    t = toks(60 + 150, cfg["vocab"], 19)
+    ref = ref_logits(cfg, w, t)
+    steps = [whole("a", t[:60], end=False)] + [{"entries": [{"id": "a", "tokens": [x], "want": [0]}]} for x in t[60:]]
+    logits, _ = run_trace(d, steps, page=16)
+    got = np.concatenate(logits)
+    err = [rel_err(got[i:i + 1], ref[i:i + 1]) for i in range(len(t))]
+    assert max(err) < TOL32, f"first bad position {int(np.argmax(np.array(err) >= TOL32))}"
+
+
+# ---- batches --------------------------------------------------------------------------------------------------------
+def test_unequal_batch_equals_each_alone(base):
+    cfg, w, d = base
+    prompts = {"x": toks(1, cfg["vocab"], 21), "y": toks(67, cfg["vocab"], 22), "z": toks(130, cfg["vocab"], 23)}
+    tails = {k: toks(n, cfg["vocab"], 30 + i) for i, (k, n) in enumerate({"x": 3, "y": 12, "z": 7}.items())}
+    steps = [{"entries": [{"id": k, "tokens": p, "want": list(range(len(p)))} for k, p in prompts.items()]}]
+    for j in range(12):
+        live = [k for k in prompts if j < len(tails[k])]
+        steps.append({"entries": [{"id": k, "tokens": [tails[k][j]], "want": [0]} for k in live],
+                      "end": [k for k in live if j == len(tails[k]) - 1]})
+    logits, _ = run_trace(d, steps, page=8, max_tokens=256)
+    for k in prompts:
+        full = prompts[k] + tails[k]
+        ref = ref_logits(cfg, w, full)
+        rows = []
+        at = 0
+        for kk, p in prompts.items():
+            if kk == k:
+                rows.append(logits[0][at:at + len(p)])
+            at += len(p)
+        for j in range(len(tails[k])):
+            live = [kk for kk in prompts if j < len(tails[kk])]
+            rows.append(logits[1 + j][live.index(k)][None])
+        assert rel_err(np.concatenate(rows), ref) < TOL32, k
+
+
+def test_pages_and_slots_are_reused(base):
+    """The pool holds one request at a time: each request runs in pages and in the slot the one before it gave back,
+    and must see nothing of it."""
+    cfg, w, d = base
+    reqs = [toks(n, cfg["vocab"], 40 + i) for i, n in enumerate([50, 33, 64, 7, 50])]
+    steps = []
+    for i, t in enumerate(reqs):
+        steps.append(whole(f"r{i}", t[:-3], end=False))
+        steps += [{"entries": [{"id": f"r{i}", "tokens": [x], "want": [0]}]} for x in t[-3:-1]]
+        steps.append({"entries": [{"id": f"r{i}", "tokens": [t[-1]], "want": [0]}], "end": [f"r{i}"]})
+    logits, _ = run_trace(d, steps, page=4, max_tokens=64, extra=["--max-seqs", "1"])
+    at = 0
+    for t in reqs:
+        got = np.concatenate(logits[at:at + 4])
+        at += 4
+        assert rel_err(got, ref_logits(cfg, w, t)) < TOL32
+
+
+def test_first_tokens_and_single_token_requests(base):
+    cfg, w, d = base
+    ts = [toks(n, cfg["vocab"], 50 + n) for n in (1, 2, 3)]
+    logits, _ = run_trace(d, [whole(f"q{i}", t) for i, t in enumerate(ts)])
+    for t, lg in zip(ts, logits):
+        assert rel_err(lg, ref_logits(cfg, w, t)) < TOL32
+
+
+# ---- bf16, generation -------------------------------------------------------------------------------------------------
+def test_bfloat16_products(base):
+    cfg, w, d = base
+    t = toks(140, cfg["vocab"], 61)
+    ref = ref_logits(cfg, w, t)
+    steps = [whole("a", t[:120], end=False)] + [{"entries": [{"id": "a", "tokens": [x], "want": [0]}]} for x in t[120:]]
+    logits, _ = run_trace(d, steps, dtype="bfloat16")
+    assert rel_err(np.concatenate(logits), ref) < TOL16
+
+
+def test_greedy_generation_through_the_scheduler(base):
+    import subprocess
+    from kuiperllama_b200 import build
+    cfg, w, d = base
+    tools = build.build_seq_tools()
+    prompts = [toks(9, cfg["vocab"], 71), toks(30, cfg["vocab"], 72), toks(2, cfg["vocab"], 73)]
+    cmd = [str(tools / "kuiper_generate"), "--model", str(d), "--dtype", "float32", "--new", "12", "--page", "8"]
+    for p in prompts:
+        cmd += ["--prompt", " ".join(map(str, p))]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = [[int(x) for x in ln.split()] for ln in r.stdout.strip().splitlines()]
+    for p, g in zip(prompts, got):
+        assert g == greedy(cfg, w, p, 12)
+
+
+def test_larger_shapes_take_the_block_paths(tmp_path):
+    """Enough tokens and wide enough layers for the tiled and grouped products (and, in bf16, the tensor-core one)."""
+    cfg = make_config(width=256, vocab=300, layers=2, heads=8, kv_heads=2, dim=64, vdim=64, experts=8, top=2, ff=128,
+                      shared_ff=256, loop=(0, 2, 2), q_temp=(0.5, 64))
+    w = make_weights(cfg, seed=77, sharp=2.0)
+    d = write_model(tmp_path, cfg, w)
+    t = toks(300, cfg["vocab"], 78)
+    ref = ref_logits(cfg, w, t)
+    want = list(range(0, 300, 7)) + [299]
+    for dtype, tol in (("float32", TOL32), ("bfloat16", TOL16)):
+        logits, _ = run_trace(d, [whole("a", t, want=want)], dtype=dtype)
+        assert rel_err(logits[0], ref[want]) < tol, dtype
