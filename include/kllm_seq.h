@@ -114,6 +114,11 @@ int kllm_seq_trace_residual(kllm_seq_engine* eng, float* residual_host);
 /* kernel launches of the last step */
 int kllm_seq_last_launches(const kllm_seq_engine* eng);
 
+/* The engine's token-block product on its own: out[T, N] (fp32) = a[T, K] . w[N, K]^T with a and w in the compute
+ * type `dtype` (device pointers).  Picks the kernel the engine would pick for this shape. */
+int kllm_seq_gemm(int32_t dtype, const void* a, const void* w, float* out, int32_t n_tokens, int32_t in_dim,
+                  int32_t out_dim, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -466,5 +466,14 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   }
   e->last_launches = static_cast<int>(launch_counter().load() - launches_before);
   CU(cudaStreamSynchronize(st));
+  if (gemm_take_error()) return KLLM_E_STATE;
+  return 0;
+}
+
+extern "C" int kllm_seq_gemm(int32_t dtype, const void* a, const void* w, float* out, int32_t n_tokens, int32_t in_dim,
+                             int32_t out_dim, void* stream) {
+  const int rc = gemm(dtype, a, w, out, n_tokens, in_dim, out_dim, static_cast<cudaStream_t>(stream));
+  if (rc != 0) return rc;
+  if (gemm_take_error()) return KLLM_E_STATE;
   return 0;
 }

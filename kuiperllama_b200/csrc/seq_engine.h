@@ -110,6 +110,8 @@ int launch_sort_pairs(const int32_t* top_idx, int n_pairs, int experts, int bloc
 // ---- seq_gemm.cu --------------------------------------------------------------------------------------------------
 // out[T, N] (fp32) = a[T, K] . w[N, K]^T, a and w in the compute type, fp32 accumulation.
 int gemm(int dtype, const void* a, const void* w, float* out, int T, int K, int N, cudaStream_t s);
+// != 0 when a bounded wait inside a tensor-core product ran out since the last call (checked after a step's sync)
+int gemm_take_error();
 // Grouped form for the routed experts: block b (of `block` rows) multiplies rows a[row_of(b, i)] with the weights of
 // expert block_expert[b]; see seq_gemm.cu.
 struct GroupedArgs {

@@ -196,7 +196,7 @@ tiled_kernel(const AT* __restrict__ a, const AT* __restrict__ w, void* __restric
 }
 
 template <typename AT>
-int gemm_t(const AT* a, const AT* w, float* out, int T, int K, int N, cudaStream_t s) {
+int gemm_t(const AT* a, const AT* w, float* out, int T, int K, int N, cudaStream_t s, bool* umma_used) {
   constexpr int V = Vec16<AT>::N;
   if (T <= 8) {
     const bool vec = (K % V) == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
@@ -215,7 +215,10 @@ int gemm_t(const AT* a, const AT* w, float* out, int T, int K, int N, cudaStream
     count_launch();
     return cuda_rc(cudaGetLastError());
   }
-  if (umma::usable<AT>(a, w, T, K, N)) return umma::launch(a, w, out, T, K, N, s);
+  if (umma::usable<AT>(a, w, T, K, N)) {
+    *umma_used = true;
+    return umma::launch(a, w, out, T, K, N, s);
+  }
   const dim3 grid((N + TN - 1) / TN, (T + TM - 1) / TM);
   tiled_kernel<AT, false, 0><<<grid, 256, 0, s>>>(a, w, out, T, K, N, nullptr, nullptr, 1);
   count_launch();
@@ -238,12 +241,19 @@ int grouped_t(const GroupedArgs& g, cudaStream_t s) {
 
 }  // namespace
 
+static bool g_umma_used;
 int gemm(int dtype, const void* a, const void* w, float* out, int T, int K, int N, cudaStream_t s) {
   if (!a || !w || !out || T <= 0 || K <= 0 || N <= 0) return KLLM_E_INVALID;
-  if (dtype == KLLM_SEQ_F32) return gemm_t(static_cast<const float*>(a), static_cast<const float*>(w), out, T, K, N, s);
+  if (dtype == KLLM_SEQ_F32) return gemm_t(static_cast<const float*>(a), static_cast<const float*>(w), out, T, K, N, s, &g_umma_used);
   if (dtype == KLLM_SEQ_BF16)
-    return gemm_t(static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(w), out, T, K, N, s);
+    return gemm_t(static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(w), out, T, K, N, s, &g_umma_used);
   return KLLM_E_INVALID;
+}
+
+int gemm_take_error() {
+  if (!g_umma_used) return 0;
+  g_umma_used = false;
+  return umma::take_error();
 }
 
 int gemm_grouped(int dtype, const GroupedArgs& g, cudaStream_t s) {

@@ -26,10 +26,10 @@ def base(tmp_path_factory):
     """Two different layers, a loop over one of them, odd sizes (dim not a multiple of 4, a value size between one
     and two key tiles of columns), a temperature step every 5 positions."""
     cfg = make_config(width=72, vocab=101, layers=3, heads=6, kv_heads=2, dim=18, vdim=40, experts=5, top=2, ff=24,
-                      shared_ff=40, loop=(1, 3, 2), q_temp=(0.7, 5))
+                      shared_ff=40, loop=(1, 3, 2), q_temp=(0.4, 5))
     cfg["layers"][2]["mixer"].update(heads=3, kv_heads=3, dim=32, vdim=72)          # no grouping, wide values
     cfg["layers"][1]["mlp"]["router"].update(experts=3, top=3)                       # every expert chosen
-    w = make_weights(cfg, seed=1, sharp=4.0)
+    w = make_weights(cfg, seed=1, sharp=2.5)
     d = write_model(tmp_path_factory.mktemp("fobo_base"), cfg, w)
     return cfg, w, d
 
@@ -193,8 +193,12 @@ def test_first_tokens_and_single_token_requests(base):
 
 
 # ---- bf16, generation -------------------------------------------------------------------------------------------------
-def test_bfloat16_products(base):
-    cfg, w, d = base
+def test_bfloat16_products(tmp_path):
+    """bf16 products round scores too: a tame softmax (no sharpening) keeps the comparison about the kernels."""
+    cfg = make_config(width=72, vocab=101, layers=2, heads=6, kv_heads=2, dim=18, vdim=40, experts=5, top=2, ff=24,
+                      shared_ff=40, loop=(0, 1, 2), q_temp=(0.2, 50))
+    w = make_weights(cfg, seed=5)
+    d = write_model(tmp_path, cfg, w)
     t = toks(140, cfg["vocab"], 61)
     ref = ref_logits(cfg, w, t)
     steps = [whole("a", t[:120], end=False)] + [{"entries": [{"id": "a", "tokens": [x], "want": [0]}]} for x in t[120:]]
