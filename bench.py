@@ -89,6 +89,10 @@ def parse_args():
     ap.add_argument("--no-secondary", action="store_true", help="N>1: skip the fp32 Llama-2-7B line (configs[4])")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the cpu_baseline leg")
     ap.add_argument("--seed", type=int, default=None)
+    ap.add_argument("--family", default=None, choices=["fobolorn"],
+                    help="measure a batched model family (prefill and decode of the sequence-batch engine beside the "
+                         "closest single-sequence model at equal size) instead of the default workload")
+    ap.add_argument("--family-sizes", default=None, help="comma-separated sizes of the family bench (s,m,debug)")
     return ap.parse_args()
 
 
@@ -677,6 +681,10 @@ def main():
                                   f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1",
                                   "--master-port", os.environ.get("MASTER_PORT", "29517"),
                                   str(Path(__file__).resolve()), *sys.argv[1:]])
+    if args.family is not None:
+        from kuiperllama_b200 import family_bench
+        family_bench.run(args, emit)
+        return
     if args.workload is None:
         args.workload = default_workload(args.gpus)
     if args.seed is None:

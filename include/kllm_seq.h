@@ -111,6 +111,19 @@ int kllm_seq_step(kllm_seq_engine* eng, int32_t n_entries, const int32_t* seqs, 
 /* Diagnostics: the next step also copies the residual stream after every layer run to host memory
  * [n_runs, tokens of the step, width]; fusions across layer runs are switched off for that step. */
 int kllm_seq_trace_residual(kllm_seq_engine* eng, float* residual_host);
+/* Measurement aid: the next step records an event after each of its phases and writes the device time spent in every
+ * phase class, in milliseconds, to phase_ms[KLLM_SEQ_PHASES] (summed over the layer runs). */
+#define KLLM_SEQ_PHASE_NORM 0       /* embedding rows, residual + layer-norm kernels */
+#define KLLM_SEQ_PHASE_IN_PROJ 1    /* q | k | v | gate product */
+#define KLLM_SEQ_PHASE_QK_PREPARE 2 /* head norms, temperature, cache scatter, gates */
+#define KLLM_SEQ_PHASE_ATTENTION 3  /* paged attention + merge of the key splits */
+#define KLLM_SEQ_PHASE_OUT_PROJ 4
+#define KLLM_SEQ_PHASE_ROUTER 5
+#define KLLM_SEQ_PHASE_EXPERTS 6    /* routed experts */
+#define KLLM_SEQ_PHASE_SHARED 7     /* shared expert */
+#define KLLM_SEQ_PHASE_HEAD 8       /* final norm of the wanted rows, classifier, argmax, copies */
+#define KLLM_SEQ_PHASES 9
+int kllm_seq_profile(kllm_seq_engine* eng, float* phase_ms);
 /* kernel launches of the last step */
 int kllm_seq_last_launches(const kllm_seq_engine* eng);
 

@@ -27,7 +27,9 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <new>
+#include <tuple>
 #include <vector>
 
 #include "../../include/kllm_seq.h"
@@ -50,11 +52,14 @@ constexpr int kGroupBlock = 64;
 inline NormW nw(const kllm_seq_norm& n) { return NormW{n.w, n.b}; }
 inline size_t elt(int dtype) { return dtype == KLLM_SEQ_BF16 ? 2 : 4; }
 
+uint64_t g_buffer_generation = 0;  // bumped whenever a workspace moves: captured graphs hold the old addresses
+
 struct DevBuf {
   void* p = nullptr;
   size_t cap = 0;
   int reserve(size_t bytes) {
     if (bytes <= cap) return 0;
+    ++g_buffer_generation;
     if (p) cudaFree(p);
     p = nullptr;
     cap = 0;
@@ -90,11 +95,36 @@ struct kllm_seq_engine {
   // per-step staging
   int32_t* pinned = nullptr;
   size_t pinned_cap = 0;
-  DevBuf idx, x, h, proj, q, gates, att, y, y2, ws, top_idx, top_w, sgate, inter, pairs_out, sort, hw, logits, amax;
+  DevBuf idx, x, h, proj, q, gates, att, y, y2, ws, top_idx, top_w, sgate, inter, pairs_out, sort, sorted_a, sorted_inter, hw, logits, amax;
   float* logits_pinned = nullptr;
   size_t logits_pinned_cap = 0;
   float* trace_host = nullptr;
   int last_launches = 0;
+  // decode steps (one token per entry) are captured once per shape and replayed: the kernels read tokens, positions
+  // and page tables from fixed device buffers, so a graph stays valid until a workspace moves
+  struct Graph {
+    cudaGraphExec_t exec = nullptr;
+    uint64_t generation = 0;
+    int nodes = 0;
+  };
+  std::map<std::tuple<int, int, int, int>, Graph> graphs;
+  bool own_stream = false;
+  bool use_graphs = true;
+  // per-phase device times of one step (kllm_seq_profile): an event after every phase, read after the step's sync
+  float* prof_out = nullptr;
+  std::vector<cudaEvent_t> prof_events;
+  std::vector<int> prof_phase;
+  size_t prof_used = 0;
+  void mark(int phase) {
+    if (!prof_out) return;
+    if (prof_used == prof_events.size()) {
+      cudaEvent_t ev;
+      if (cudaEventCreate(&ev) != cudaSuccess) return;
+      prof_events.push_back(ev);
+    }
+    cudaEventRecord(prof_events[prof_used++], stream);
+    prof_phase.push_back(phase);
+  }
   // limits over the layers
   int max_proj = 0, max_q = 0, max_att = 0, max_heads = 0, max_top = 0, max_ff = 0, max_sff = 0;
 
@@ -104,6 +134,9 @@ struct kllm_seq_engine {
     if (table_dev) cudaFree(table_dev);
     if (pinned) cudaFreeHost(pinned);
     if (logits_pinned) cudaFreeHost(logits_pinned);
+    for (cudaEvent_t ev : prof_events) cudaEventDestroy(ev);
+    for (auto& g : graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+    if (own_stream && stream) cudaStreamDestroy(stream);
   }
 };
 
@@ -155,6 +188,14 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
   e->d.run_layer = e->run_layer.data();
   e->d.run_add = e->run_add.data();
   e->stream = static_cast<cudaStream_t>(stream);
+  if (e->stream == nullptr) {  // a stream of its own: the legacy default stream cannot be captured
+    if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) {
+      delete e;
+      return KLLM_E_NODEVICE;
+    }
+    e->own_stream = true;
+  }
+  if (const char* g = getenv("KLLM_SEQ_GRAPHS")) e->use_graphs = g[0] != '0';
   e->page = desc->page_tokens > 0 ? desc->page_tokens : kDefaultPage;
   // every live sequence may leave its last page partly empty
   e->n_pages = (desc->max_tokens + e->page - 1) / e->page + desc->max_seqs;
@@ -234,6 +275,12 @@ extern "C" int kllm_seq_free_pages(const kllm_seq_engine* e) {
 extern "C" int kllm_seq_trace_residual(kllm_seq_engine* e, float* residual_host) {
   if (!e) return KLLM_E_INVALID;
   e->trace_host = residual_host;
+  return 0;
+}
+
+extern "C" int kllm_seq_profile(kllm_seq_engine* e, float* phase_ms) {
+  if (!e) return KLLM_E_INVALID;
+  e->prof_out = phase_ms;
   return 0;
 }
 
@@ -328,7 +375,10 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   {
     const int tiles = (max_ctx + kAttnKeys - 1) / kAttnKeys;
     const int ctas = n_entries * ((max_count * 8 + kAttnRows - 1) / kAttnRows);
-    if (ctas < 64) splits = std::max(1, std::min({tiles, 32, 128 / std::max(1, ctas)}));
+    if (ctas < 64) {
+      const int want = std::max(1, std::min({tiles, 32, 128 / std::max(1, ctas)}));
+      while (splits < want) splits *= 2;  // a power of two: few distinct launch shapes as a context grows
+    }
   }
   const size_t Ts = static_cast<size_t>(T);
   RC(e->x.reserve(Ts * W * 4));
@@ -353,6 +403,11 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
     RC(e->inter.reserve(Ts * e->max_ff * es));
     if (grouped) RC(e->pairs_out.reserve(Ts * e->max_top * W * 4));
   }
+  if (n_want > 0) {
+    RC(e->hw.reserve(static_cast<size_t>(n_want) * W * es));
+    RC(e->logits.reserve(static_cast<size_t>(n_want) * d.vocab * 4));
+    RC(e->amax.reserve(static_cast<size_t>(n_want) * 4));
+  }
   float* x = static_cast<float*>(e->x.p);
   float* proj = static_cast<float*>(e->proj.p);
   float* y = static_cast<float*>(e->y.p);
@@ -360,7 +415,12 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   const bool tracing = e->trace_host != nullptr;
 
   // ---- device: the layer runs -------------------------------------------------------------------------------------
+  e->prof_used = 0;
+  e->prof_phase.clear();
+  e->mark(-1);
+  auto run_device = [&]() -> int {
   RC(launch_embed(dtype, d.embed, d_tok, x, T, W, st));
+  e->mark(KLLM_SEQ_PHASE_NORM);
   bool pre_done = false;  // the previous run's last kernel already produced this run's h (and added its vector)
   for (int r = 0; r < d.n_runs; ++r) {
     const kllm_seq_layer& L = e->layers[e->run_layer[r]];
@@ -372,16 +432,21 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       a.x = x, a.add = e->run_add[r] >= 0 ? d.run_vectors + static_cast<size_t>(e->run_add[r]) * W : nullptr;
       a.pre = nw(L.pre_mixer), a.out = e->h.p, a.T = T, a.width = W, a.dtype = dtype, a.eps = d.norm_eps;
       RC(launch_resid_norm(a, st));
+      e->mark(KLLM_SEQ_PHASE_NORM);
     }
     pre_done = false;
     const int n_proj = A.heads * A.dim + A.kv_heads * (A.dim + A.vdim) + (A.gate ? A.heads : 0);
     RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, n_proj, st));
+    e->mark(KLLM_SEQ_PHASE_IN_PROJ);
     RC(launch_qk_prepare(dtype, shape, proj, A.q_norm_w, A.k_norm_w, d.norm_eps, d_seq, d_pos, e->q.p,
                          static_cast<float*>(e->gates.p), kv, T, st));
+    e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
     RC(launch_attention(dtype, shape, e->q.p, static_cast<const float*>(e->gates.p), kv, n_entries, d_first, d_count,
                         d_eseq, d_pos0, max_count, max_ctx, splits, static_cast<float*>(e->ws.p), e->att.p, T, d_seq,
                         d_pos, st));
+    e->mark(KLLM_SEQ_PHASE_ATTENTION);
     RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
+    e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
 
     // what follows this layer run: the next run's vector and pre-norm can ride on this run's last kernel
     const bool last = r + 1 == d.n_runs;
@@ -396,6 +461,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       a.x = x, a.y1 = y, a.post = nw(L.post_mixer), a.T = T, a.width = W, a.dtype = dtype, a.eps = d.norm_eps;
       if (next_pre.w) a.add = next_add, a.pre = next_pre, a.out = e->h.p, pre_done = true;
       RC(launch_resid_norm(a, st));
+      e->mark(KLLM_SEQ_PHASE_NORM);
     } else {
       const kllm_seq_moe& M = L.moe;
       {
@@ -403,12 +469,14 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
         a.x = x, a.y1 = y, a.post = nw(L.post_mixer), a.pre = nw(L.pre_ff), a.out = e->h.p, a.T = T, a.width = W;
         a.dtype = dtype, a.eps = d.norm_eps;
         RC(launch_resid_norm(a, st));
+        e->mark(KLLM_SEQ_PHASE_NORM);
       }
       int32_t* top_idx = static_cast<int32_t*>(e->top_idx.p);
       float* top_w = static_cast<float*>(e->top_w.p);
       float* sgate = static_cast<float*>(e->sgate.p);
       RC(launch_router(dtype, e->h.p, M.w_router, M.shared_ff > 0 ? M.w_shared_gate : nullptr, M.experts, M.top,
                        M.router_scale, top_idx, top_w, sgate, T, W, st));
+      e->mark(KLLM_SEQ_PHASE_ROUTER);
       if (!grouped) {
         RC(launch_expert_gate_up(dtype, e->h.p, M.gate_up, top_idx, e->inter.p, T, M.top, M.ff, W, st));
         RC(launch_expert_down(dtype, e->inter.p, M.down, top_idx, top_w, y, T, M.top, M.ff, W, st));
@@ -422,50 +490,112 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
         int32_t* block_expert = sorted + cap;
         RC(launch_sort_pairs(top_idx, n_pairs, M.experts, kGroupBlock, counts_d, sorted, block_expert, cap, st));
         GroupedArgs g{};
-        g.a = e->h.p, g.w = M.gate_up, g.sorted_pair = sorted, g.block_expert = block_expert, g.a_row_div = M.top;
-        g.n_blocks = n_blocks, g.block = kGroupBlock, g.K = W, g.N = M.ff, g.epilogue = 1, g.out = e->inter.p;
-        RC(gemm_grouped(dtype, g, st));
-        g.a = e->inter.p, g.w = M.down, g.a_row_div = 1, g.K = M.ff, g.N = W, g.epilogue = 0, g.out = e->pairs_out.p;
-        RC(gemm_grouped(dtype, g, st));
+        g.sorted_pair = sorted, g.block_expert = block_expert, g.n_blocks = n_blocks, g.block = kGroupBlock;
+        g.experts = M.experts;
+        if (grouped_tensor_core_usable(dtype, W, M.ff)) {
+          // rows in sorted order: a gathered copy of h, the expert's inner activations, then scattered back by pair
+          RC(e->sorted_a.reserve(static_cast<size_t>(cap) * W * es));
+          RC(e->sorted_inter.reserve(static_cast<size_t>(cap) * M.ff * es));
+          RC(gather_rows_bf16(e->h.p, sorted, M.top, e->sorted_a.p, cap, W, st));
+          g.sorted_layout = 1;
+          g.a = e->sorted_a.p, g.w = M.gate_up, g.K = W, g.N = M.ff, g.epilogue = 1, g.out = e->sorted_inter.p;
+          RC(gemm_grouped(dtype, g, st));
+          g.a = e->sorted_inter.p, g.w = M.down, g.K = M.ff, g.N = W, g.epilogue = 0, g.out = e->pairs_out.p;
+          RC(gemm_grouped(dtype, g, st));
+        } else {
+          g.a = e->h.p, g.w = M.gate_up, g.a_row_div = M.top, g.K = W, g.N = M.ff, g.epilogue = 1, g.out = e->inter.p;
+          RC(gemm_grouped(dtype, g, st));
+          g.a = e->inter.p, g.w = M.down, g.a_row_div = 1, g.K = M.ff, g.N = W, g.epilogue = 0, g.out = e->pairs_out.p;
+          RC(gemm_grouped(dtype, g, st));
+        }
         RC(launch_combine_pairs(static_cast<const float*>(e->pairs_out.p), top_w, y, T, M.top, W, st));
       }
+      e->mark(KLLM_SEQ_PHASE_EXPERTS);
       const bool shared = M.shared_ff > 0;
       if (shared) {
         RC(gemm(dtype, e->h.p, M.shared_gate_up, proj, T, W, 2 * M.shared_ff, st));
         RC(launch_silu_mul(dtype, proj, e->att.p, T, M.shared_ff, st));
         RC(gemm(dtype, e->att.p, M.shared_down, y2, T, M.shared_ff, W, st));
+        e->mark(KLLM_SEQ_PHASE_SHARED);
       }
       ResidNormArgs a{};
       a.x = x, a.y1 = y, a.y2 = shared ? y2 : nullptr, a.s2 = shared && M.w_shared_gate ? sgate : nullptr;
       a.post = nw(L.post_ff), a.T = T, a.width = W, a.dtype = dtype, a.eps = d.norm_eps;
       if (next_pre.w) a.add = next_add, a.pre = next_pre, a.out = e->h.p, pre_done = true;
       RC(launch_resid_norm(a, st));
+      e->mark(KLLM_SEQ_PHASE_NORM);
     }
     if (tracing)
       CU(cudaMemcpyAsync(e->trace_host + static_cast<size_t>(r) * T * W, x, Ts * W * 4, cudaMemcpyDeviceToHost, st));
   }
-  e->trace_host = nullptr;
 
   // ---- the wanted rows: final norm, classifier, greedy id -------------------------------------------------------
   if (n_want > 0) {
-    RC(e->hw.reserve(static_cast<size_t>(n_want) * W * es));
-    RC(e->logits.reserve(static_cast<size_t>(n_want) * d.vocab * 4));
-    RC(e->amax.reserve(static_cast<size_t>(n_want) * 4));
     ResidNormArgs a{};
     a.x = x, a.pre = nw(d.final_norm), a.out = e->hw.p, a.rows = d_want, a.T = n_want, a.width = W, a.dtype = dtype;
     a.eps = d.norm_eps;
     RC(launch_resid_norm(a, st));
     float* lg = static_cast<float*>(e->logits.p);
     RC(gemm(dtype, e->hw.p, d.head, lg, n_want, W, d.vocab, st));
-    if (argmax_host) {
-      RC(launch_argmax_rows(lg, static_cast<int32_t*>(e->amax.p), n_want, d.vocab, st));
-      CU(cudaMemcpyAsync(argmax_host, e->amax.p, static_cast<size_t>(n_want) * 4, cudaMemcpyDeviceToHost, st));
-    }
-    if (logits_host)
-      CU(cudaMemcpyAsync(logits_host, lg, static_cast<size_t>(n_want) * d.vocab * 4, cudaMemcpyDeviceToHost, st));
+    if (argmax_host) RC(launch_argmax_rows(lg, static_cast<int32_t*>(e->amax.p), n_want, d.vocab, st));
   }
+  return 0;
+  };  // run_device
+
+  bool all_single = !tracing && e->prof_out == nullptr && e->use_graphs && T <= 32;
+  for (int i = 0; i < n_entries && all_single; ++i) all_single = counts[i] == 1;
+  bool replayed = false;
+  if (all_single) {
+    const auto key = std::make_tuple(n_entries, n_want, splits, argmax_host ? 1 : 0);
+    kllm_seq_engine::Graph& g = e->graphs[key];
+    if (g.exec != nullptr && g.generation != g_buffer_generation) {
+      cudaGraphExecDestroy(g.exec);
+      g.exec = nullptr;
+    }
+    if (g.exec == nullptr) {
+      const uint64_t before = launch_counter().load();
+      cudaGraph_t graph = nullptr;
+      if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+        const int rc = run_device();
+        const cudaError_t ce = cudaStreamEndCapture(st, &graph);
+        if (rc == 0 && ce == cudaSuccess && graph != nullptr &&
+            cudaGraphInstantiate(&g.exec, graph, 0) == cudaSuccess) {
+          g.generation = g_buffer_generation;
+          g.nodes = static_cast<int>(launch_counter().load() - before);
+        } else {
+          g.exec = nullptr;
+          cudaGetLastError();
+        }
+        if (graph) cudaGraphDestroy(graph);
+      }
+      launch_counter().fetch_sub(launch_counter().load() - before);  // captured, not launched
+    }
+    if (g.exec != nullptr) {
+      CU(cudaGraphLaunch(g.exec, st));
+      count_launch(static_cast<uint64_t>(g.nodes));
+      replayed = true;
+    }
+  }
+  if (!replayed) RC(run_device());
+  e->trace_host = nullptr;
+  if (n_want > 0) {
+    if (argmax_host)
+      CU(cudaMemcpyAsync(argmax_host, e->amax.p, static_cast<size_t>(n_want) * 4, cudaMemcpyDeviceToHost, st));
+    if (logits_host)
+      CU(cudaMemcpyAsync(logits_host, e->logits.p, static_cast<size_t>(n_want) * d.vocab * 4, cudaMemcpyDeviceToHost, st));
+  }
+  e->mark(KLLM_SEQ_PHASE_HEAD);
   e->last_launches = static_cast<int>(launch_counter().load() - launches_before);
   CU(cudaStreamSynchronize(st));
+  if (e->prof_out) {
+    for (int i = 0; i < KLLM_SEQ_PHASES; ++i) e->prof_out[i] = 0.f;
+    for (size_t i = 1; i < e->prof_used; ++i) {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, e->prof_events[i - 1], e->prof_events[i]) == cudaSuccess && e->prof_phase[i] >= 0)
+        e->prof_out[e->prof_phase[i]] += ms;
+    }
+    e->prof_out = nullptr;
+  }
   if (gemm_take_error()) return KLLM_E_STATE;
   return 0;
 }

@@ -125,8 +125,16 @@ struct GroupedArgs {
   // weights hold ff gate rows, then ff up rows; N = ff)
   int epilogue;
   void* out;
+  // tensor-core form (bf16): `a` is already in sorted order [n_blocks * block, K] and epilogue 1 writes its result in
+  // sorted order too; `experts` sizes the weight map
+  int sorted_layout;
+  int experts;
 };
 int gemm_grouped(int dtype, const GroupedArgs& g, cudaStream_t s);
+// bf16 only: can the grouped products of an expert layer (K = width, then K = ff) run on the tensor cores?
+bool grouped_tensor_core_usable(int dtype, int width, int ff);
+// hs[i] = a[sorted_pair[i] / div] (zero rows where sorted_pair[i] < 0), bf16, K % 8 == 0
+int gather_rows_bf16(const void* a, const int32_t* sorted_pair, int div, void* out, int rows, int K, cudaStream_t s);
 
 inline int cuda_rc(cudaError_t e) { return static_cast<int>(e); }
 }  // namespace seq

@@ -256,7 +256,26 @@ int gemm_take_error() {
   return umma::take_error();
 }
 
+bool grouped_tensor_core_usable(int dtype, int width, int ff) {
+  return dtype == KLLM_SEQ_BF16 && umma::grouped_usable(width, ff) && umma::grouped_usable(ff, width);
+}
+
+int gather_rows_bf16(const void* a, const int32_t* sorted_pair, int div, void* out, int rows, int K, cudaStream_t s) {
+  if ((K % 8) != 0) return KLLM_E_UNSUPPORTED;
+  umma::gather_rows_kernel<<<rows, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(a), sorted_pair, div,
+                                               static_cast<__nv_bfloat16*>(out), K);
+  count_launch();
+  return cuda_rc(cudaGetLastError());
+}
+
 int gemm_grouped(int dtype, const GroupedArgs& g, cudaStream_t s) {
+  if (g.sorted_layout) {
+    if (dtype != KLLM_SEQ_BF16 || g.block != umma::GBN) return KLLM_E_INVALID;
+    g_umma_used = true;
+    if (g.epilogue == 1)
+      return umma::launch_grouped<1>(g.a, g.w, g.out, g.sorted_pair, g.block_expert, g.n_blocks, g.experts, g.K, g.N, s);
+    return umma::launch_grouped<0>(g.a, g.w, g.out, g.sorted_pair, g.block_expert, g.n_blocks, g.experts, g.K, g.N, s);
+  }
   if (dtype == KLLM_SEQ_F32) return grouped_t<float>(g, s);
   if (dtype == KLLM_SEQ_BF16) return grouped_t<__nv_bfloat16>(g, s);
   return KLLM_E_INVALID;

@@ -70,22 +70,63 @@ template <> struct VecOf<__nv_bfloat16> {
 };
 
 // dot of a weight row (compute type, global) with an fp32 vector in shared memory, spread over the warp's lanes;
-// every lane returns the total.
+// every lane returns the total.  Four 16-byte loads are in flight per lane before the first multiply.
 template <typename AT>
 __device__ __forceinline__ float warp_dot(const AT* __restrict__ w, const float* __restrict__ xs, int K, int lane) {
   constexpr int V = VecOf<AT>::N;
   float acc = 0.f;
   if ((K % V) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
-    for (int k = lane * V; k < K; k += 32 * V) {
-      float f[V];
-      VecOf<AT>::load(w + k, f);
+    for (int k = lane * V; k < K; k += 4 * 32 * V) {
+      float f[4][V];
 #pragma unroll
-      for (int i = 0; i < V; ++i) acc = fmaf(f[i], xs[k + i], acc);
+      for (int j = 0; j < 4; ++j)
+        if (k + j * 32 * V < K) VecOf<AT>::load(w + k + j * 32 * V, f[j]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (k + j * 32 * V < K) {
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc = fmaf(f[j][i], xs[k + j * 32 * V + i], acc);
+        }
     }
   } else {
     for (int k = lane; k < K; k += 32) acc = fmaf(to_f(w[k]), xs[k], acc);
   }
   return warp_sum(acc);
+}
+// two rows against the same vector (a gate row and its up row)
+template <typename AT>
+__device__ __forceinline__ void warp_dot2(const AT* __restrict__ w0, const AT* __restrict__ w1,
+                                          const float* __restrict__ xs, int K, int lane, float& r0, float& r1) {
+  constexpr int V = VecOf<AT>::N;
+  float a0 = 0.f, a1 = 0.f;
+  if ((K % V) == 0 && ((reinterpret_cast<uintptr_t>(w0) | reinterpret_cast<uintptr_t>(w1)) & 15) == 0) {
+    for (int k = lane * V; k < K; k += 2 * 32 * V) {
+      float f[2][2][V];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        if (k + j * 32 * V < K) {
+          VecOf<AT>::load(w0 + k + j * 32 * V, f[j][0]);
+          VecOf<AT>::load(w1 + k + j * 32 * V, f[j][1]);
+        }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        if (k + j * 32 * V < K) {
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            const float x = xs[k + j * 32 * V + i];
+            a0 = fmaf(f[j][0][i], x, a0);
+            a1 = fmaf(f[j][1][i], x, a1);
+          }
+        }
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) {
+      a0 = fmaf(to_f(w0[k]), xs[k], a0);
+      a1 = fmaf(to_f(w1[k]), xs[k], a1);
+    }
+  }
+  r0 = warp_sum(a0);
+  r1 = warp_sum(a1);
 }
 
 // ---- embedding ----------------------------------------------------------------------------------------------------
@@ -211,7 +252,10 @@ __global__ void qk_prepare_kernel(AttnShape a, const float* __restrict__ qkvg, c
 // shared memory in fp32; scores, the running maximum / sum and the output accumulators are fp32 (online softmax).
 // The partial result of a split is (m, l, o[vdim]) per row; attention_merge_kernel combines the splits, applies the
 // output gate and converts to the compute type.
-template <typename AT, int C>
+// SPARSE: the launch has tiles with few rows (decode steps: heads / kv_heads rows) -- rows that do not exist are skipped
+// and the key tiles come in with 16-byte loads; otherwise (prompts) every loop is fully unrolled over the 16 rows of a
+// thread.
+template <typename AT, int C, bool SPARSE>
 __global__ void __launch_bounds__(kAttnThreads)
 attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_t* __restrict__ ent_first,
                  const int32_t* __restrict__ ent_count, const int32_t* __restrict__ ent_seq,
@@ -265,10 +309,36 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
   const AT* kbase = static_cast<const AT*>(kv.k);
   const AT* vbase = static_cast<const AT*>(kv.v);
   const int32_t* table = kv.table + static_cast<size_t>(seq) * kv.table_stride;
+  const bool vec_tiles = SPARSE && (a.dim % VecOf<AT>::N) == 0 && (a.vdim % VecOf<AT>::N) == 0;
+  // rows of this thread that exist (a decode step fills only heads / kv_heads rows of the tile)
+  const int my_rows = max(0, min(static_cast<int>(kAttnRows / (kAttnThreads / kAttnKeys)),
+                                 rows_here - (tid / kAttnKeys) * (kAttnRows / (kAttnThreads / kAttnKeys))));
 
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
     const int k0 = tile * kAttnKeys;
     __syncthreads();  // previous tile's K, V, S are no longer read
+    if (vec_tiles) {  // 16-byte loads: a key's row is dim / V chunks
+      constexpr int V = VecOf<AT>::N;
+      const int kc = a.dim / V, vc = a.vdim / V;
+      for (int idx = tid; idx < kAttnKeys * (kc + vc); idx += kAttnThreads) {
+        const int j = idx / (kc + vc), c = idx % (kc + vc);
+        const int kj = k0 + j;
+        float f[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) f[i] = 0.f;
+        if (kj <= pmax) {
+          const size_t slot = static_cast<size_t>(table[kj / kv.page]) * kv.page + kj % kv.page;
+          if (c < kc) VecOf<AT>::load(kbase + (slot * a.kv_heads + g) * a.dim + c * V, f);
+          else VecOf<AT>::load(vbase + (slot * a.kv_heads + g) * a.vdim + (c - kc) * V, f);
+        }
+        float* dst = c < kc ? Ks + j * dk + c * V : Vs + j * a.vdim + (c - kc) * V;
+#pragma unroll
+        for (int i = 0; i < V; ++i) dst[i] = f[i];
+      }
+      if (dk > a.dim)
+        for (int idx = tid; idx < kAttnKeys * (dk - a.dim); idx += kAttnThreads)
+          Ks[(idx / (dk - a.dim)) * dk + a.dim + idx % (dk - a.dim)] = 0.f;
+    } else {
     for (int j = warp; j < kAttnKeys; j += kAttnThreads / 32) {
       const int kj = k0 + j;
       float* kd = Ks + j * dk;
@@ -284,6 +354,7 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
         for (int d = lane; d < a.vdim; d += 32) vd[d] = 0.f;
       }
     }
+    }
     __syncthreads();
     {  // scores
       float sc[RPT];
@@ -294,6 +365,7 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
         const float k0v = kp[d], k1v = kp[d + 1], k2v = kp[d + 2], k3v = kp[d + 3];
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
+          if (SPARSE && i >= my_rows) break;
           const float4 qv = *reinterpret_cast<const float4*>(Qs + (rg * RPT + i) * dq + d);
           sc[i] = fmaf(qv.x, k0v, sc[i]);
           sc[i] = fmaf(qv.y, k1v, sc[i]);
@@ -310,7 +382,7 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
       }
     }
     __syncthreads();
-    for (int r = warp; r < kAttnRows; r += kAttnThreads / 32) {  // online softmax, a warp per row
+    for (int r = warp; r < (SPARSE ? rows_here : kAttnRows); r += kAttnThreads / 32) {  // online softmax, a warp per row
       const float v0 = Ss[r * kAttnKeys + lane], v1 = Ss[r * kAttnKeys + lane + 32];
       const float m_old = m_s[r];
       const float m_new = fmaxf(m_old, warp_max(fmaxf(v0, v1)));
@@ -332,6 +404,7 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
+      if (SPARSE && i >= my_rows) break;
       const float al = al_s[rg * RPT + i];
 #pragma unroll
       for (int c = 0; c < C; ++c) acc[i][c] *= al;
@@ -347,6 +420,7 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
         }
 #pragma unroll
       for (int i = 0; i < RPT; ++i) {
+        if (SPARSE && i >= my_rows) break;
         const float4 p = *reinterpret_cast<const float4*>(Ss + (rg * RPT + i) * kAttnKeys + j);
 #pragma unroll
         for (int c = 0; c < C; ++c) {
@@ -404,31 +478,31 @@ __global__ void attention_merge_kernel(int heads, int vdim, int splits, const fl
 }
 
 // ---- router ---------------------------------------------------------------------------------------------------------
+// One CTA per token: the warps share the experts' logits (a warp per expert row, fp32 weights), then warp 0 does the
+// softmax over all experts and picks the top-k.
 template <typename AT>
 __global__ void router_kernel(const AT* __restrict__ h, const float* __restrict__ w_router,
                               const float* __restrict__ w_sg, int experts, int top, float scale,
                               int32_t* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ sgate, int T,
                               int width) {
-  extern __shared__ float sm[];  // [warps][experts]
+  extern __shared__ float sm[];  // [experts] logits, then [width] the token's row in fp32
+  float* z = sm;
+  float* xs = sm + experts;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const int t = blockIdx.x * nw + warp;
-  if (t >= T) return;
-  float* z = sm + warp * experts;
+  const int t = blockIdx.x;
   const AT* x = h + static_cast<size_t>(t) * width;
-  for (int e = 0; e < experts; ++e) {
-    const float* w = w_router + static_cast<size_t>(e) * width;
-    float acc = 0.f;
-    for (int k = lane; k < width; k += 32) acc = fmaf(w[k], to_f(x[k]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) z[e] = acc;
+  for (int k = threadIdx.x; k < width; k += blockDim.x) xs[k] = to_f(x[k]);
+  __syncthreads();
+  for (int e = warp; e < experts + (w_sg ? 1 : 0); e += nw) {
+    const float* w = e < experts ? w_router + static_cast<size_t>(e) * width : w_sg;
+    const float acc = warp_dot<float>(w, xs, width, lane);
+    if (lane == 0) {
+      if (e < experts) z[e] = acc;
+      else sgate[t] = 1.0f / (1.0f + expf(-acc));
+    }
   }
-  if (w_sg) {
-    float acc = 0.f;
-    for (int k = lane; k < width; k += 32) acc = fmaf(w_sg[k], to_f(x[k]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) sgate[t] = 1.0f / (1.0f + expf(-acc));
-  }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float mx = -INFINITY;
   for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
   mx = warp_max(mx);
@@ -465,8 +539,7 @@ __global__ void router_kernel(const AT* __restrict__ h, const float* __restrict_
     __syncwarp();
   }
   const float inv = scale / (chosen_sum + 1e-20f);
-  if (lane < top) top_w[static_cast<size_t>(t) * top + lane] *= inv;
-  for (int k = lane + 32; k < top; k += 32) top_w[static_cast<size_t>(t) * top + k] *= inv;
+  for (int k = lane; k < top; k += 32) top_w[static_cast<size_t>(t) * top + k] *= inv;
 }
 
 // ---- routed experts, pair by pair ----------------------------------------------------------------------------------
@@ -484,8 +557,8 @@ __global__ void expert_gate_up_kernel(const AT* __restrict__ h, const AT* __rest
   const AT* wu = wg + static_cast<size_t>(ff) * width;
   const int f_end = min(ff, (blockIdx.y + 1) * kPairRows);
   for (int f = blockIdx.y * kPairRows + warp; f < f_end; f += nw) {
-    const float gv = warp_dot(wg + static_cast<size_t>(f) * width, xs, width, lane);
-    const float uv = warp_dot(wu + static_cast<size_t>(f) * width, xs, width, lane);
+    float gv, uv;
+    warp_dot2(wg + static_cast<size_t>(f) * width, wu + static_cast<size_t>(f) * width, xs, width, lane, gv, uv);
     if (lane == 0) inter[static_cast<size_t>(pair) * ff + f] = from_f<AT>(gv / (1.0f + expf(-gv)) * uv);
   }
 }
@@ -649,8 +722,8 @@ size_t attention_workspace_bytes(const AttnShape& a, int T, int splits) {
   return static_cast<size_t>(T) * a.heads * splits * (a.vdim + 2) * sizeof(float);
 }
 
-template <typename AT, int C>
-static int launch_attention_c(const AttnShape& a, const void* q, const PagedKV& kv, int n_entries,
+template <typename AT, int C, bool SPARSE>
+static int launch_attention_cs(const AttnShape& a, const void* q, const PagedKV& kv, int n_entries,
                               const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
                               const int32_t* ent_pos0, int max_count, int splits, float* ws, cudaStream_t s) {
   const int dq = (a.dim + 3) & ~3;
@@ -659,16 +732,27 @@ static int launch_attention_c(const AttnShape& a, const void* q, const PagedKV& 
   if (smem > 220 * 1024) return KLLM_E_UNSUPPORTED;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
-    const cudaError_t e = cudaFuncSetAttribute(attention_kernel<AT, C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    const cudaError_t e = cudaFuncSetAttribute(attention_kernel<AT, C, SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                static_cast<int>(smem));
     if (e != cudaSuccess) return cuda_rc(e);
     configured = smem;
   }
   const int rep = a.heads / a.kv_heads;
   const dim3 grid((max_count * rep + kAttnRows - 1) / kAttnRows, n_entries * a.kv_heads, splits);
-  attention_kernel<AT, C><<<grid, kAttnThreads, smem, s>>>(a, static_cast<const AT*>(q), kv, ent_first, ent_count,
+  attention_kernel<AT, C, SPARSE><<<grid, kAttnThreads, smem, s>>>(a, static_cast<const AT*>(q), kv, ent_first, ent_count,
                                                           ent_seq, ent_pos0, splits, ws);
   return done();
+}
+
+template <typename AT, int C>
+static int launch_attention_c(const AttnShape& a, const void* q, const PagedKV& kv, int n_entries,
+                              const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
+                              const int32_t* ent_pos0, int max_count, int splits, float* ws, cudaStream_t s) {
+  if (max_count * (a.heads / a.kv_heads) < kAttnRows)
+    return launch_attention_cs<AT, C, true>(a, q, kv, n_entries, ent_first, ent_count, ent_seq, ent_pos0, max_count, splits,
+                                            ws, s);
+  return launch_attention_cs<AT, C, false>(a, q, kv, n_entries, ent_first, ent_count, ent_seq, ent_pos0, max_count, splits,
+                                           ws, s);
 }
 
 int launch_attention(int dtype, const AttnShape& a, const void* q, const float* gates, const PagedKV& kv,
@@ -700,12 +784,10 @@ int launch_attention(int dtype, const AttnShape& a, const void* q, const float* 
 int launch_router(int dtype, const void* h, const float* w_router, const float* w_sg, int experts, int top,
                   float scale, int32_t* top_idx, float* top_w, float* sgate, int T, int width, cudaStream_t s) {
   if (top > experts || experts <= 0 || top <= 0) return KLLM_E_INVALID;
-  const int warps = 4;
-  const size_t smem = static_cast<size_t>(warps) * experts * sizeof(float);
+  const size_t smem = (static_cast<size_t>(experts) + width) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
-  KLLM_SEQ_DISPATCH(dtype, (router_kernel<AT><<<(T + warps - 1) / warps, warps * 32, smem, s>>>(
-                               static_cast<const AT*>(h), w_router, w_sg, experts, top, scale, top_idx, top_w, sgate, T,
-                               width)));
+  KLLM_SEQ_DISPATCH(dtype, (router_kernel<AT><<<T, 256, smem, s>>>(static_cast<const AT*>(h), w_router, w_sg, experts, top,
+                                                                  scale, top_idx, top_w, sgate, T, width)));
   return done();
 }
 
@@ -744,7 +826,7 @@ int launch_silu_mul(int dtype, const float* gu, void* out, int T, int ff, cudaSt
 }
 
 int launch_argmax_rows(const float* logits, int32_t* out, int rows, int vocab, cudaStream_t s) {
-  argmax_rows_kernel<<<rows, 256, 0, s>>>(logits, out, vocab);
+  argmax_rows_kernel<<<rows, 1024, 0, s>>>(logits, out, vocab);
   return done();
 }
 

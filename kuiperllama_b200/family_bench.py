@@ -1,0 +1,238 @@
+"""`bench.py --family fobolorn`: prefill and decode throughput of the Fobolorn family (sequence-batch engine) at sizes
+that resemble a real model's layers, random weights, beside the closest existing model -- the Llama family of the
+single-sequence decoder -- at equal width, heads, active feed-forward size and number of layer runs.
+
+What is timed.  A step is the call a server makes: kllm_seq_step() with token ids in host memory and the greedy ids
+read back to host memory, blocking -- so every number here is end to end.  Between timed steps a buffer larger than
+L2 is written.  Per-phase device times come from the engine's own events (kllm_seq_profile) in a separate step.
+Roofline fractions use MEASURED_PEAKS.json (copy bandwidth, cuBLAS bf16) and say which.
+
+Like kernels side by side (same shapes, CUDA events, L2 flushed):
+   token-block product   kllm_seq_gemm bf16 (tcgen05 kind::f16)   vs   kllm_gemm_tf32 (tcgen05 kind::tf32)
+   one-row product       kllm_seq_gemm, 1 token (rows kernel)     vs   kllm_gemv_f32
+"""
+from __future__ import annotations
+
+import json
+import statistics
+import time
+from pathlib import Path
+
+from .sequence import BF16, F32, FobolornShape, SeqEngine, load_seq_library
+
+ROOT = Path(__file__).resolve().parent.parent
+
+SIZES = {
+    # width 1024: 16 heads of 64 over 4 kv heads, 16 experts of 512 (2 active) + shared 1024; 4 layers, 2 of them twice
+    "s": FobolornShape("fobolorn-s", 1024, 32000, 4, (1, 3, 2), 16, 4, 64, 64, 16, 2, 512, 1024),
+    # width 2048: 16 heads of 128 over 4 kv heads, 32 experts of 768 (4 active) + shared 2048
+    "m": FobolornShape("fobolorn-m", 2048, 32000, 4, (1, 3, 2), 16, 4, 128, 128, 32, 4, 768, 2048),
+    "debug": FobolornShape("fobolorn-debug", 256, 4096, 3, (1, 3, 2), 4, 2, 64, 64, 8, 2, 128, 256),
+}
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class Flusher:
+    def __init__(self, torch):
+        self.buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def __call__(self):
+        self.buf.add_(1)
+
+
+def time_events(torch, fn, flush, reps=5, warm=3):
+    for _ in range(warm):
+        fn()
+    ms = []
+    for _ in range(reps):
+        flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms.append(a.elapsed_time(b))
+    return statistics.median(ms)
+
+
+def bench_engine(torch, shape, dtype, prompt_len, ctx, batches, steps, warm, flush, hbm, tf):
+    es = 2 if dtype == BF16 else 4
+    eng = SeqEngine(shape, dtype, max_tokens=max(prompt_len, max(batches) * (ctx + steps + warm + 8)) + 64,
+                    max_seqs=max(batches) + 1, seed=7)
+    g = torch.Generator().manual_seed(1)
+
+    def toks(n):
+        return torch.randint(0, shape.vocab, (n,), generator=g).tolist()
+    out = {"dtype": "bf16" if dtype == BF16 else "fp32"}
+    # ---- prefill: one sequence of prompt_len tokens per step -----------------------------------------------------
+    times = []
+    for i in range(warm + steps):
+        s = eng.open()
+        t = toks(prompt_len)
+        flush()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        eng.step([(s, t)])
+        dt = time.perf_counter() - t0
+        eng.close_seq(s)
+        if i >= warm:
+            times.append(dt)
+    s = eng.open()
+    _, ph = eng.step([(s, toks(prompt_len))], profile=True)
+    launches = eng.launches()
+    eng.close_seq(s)
+    sec = statistics.median(times)
+    flops = shape.flops_per_token() * prompt_len + \
+        2 * prompt_len * prompt_len / 2 * (shape.dim + shape.vdim) * shape.heads * shape.runs
+    out["prefill"] = {"tokens": prompt_len, "tok_s": prompt_len / sec, "ms": sec * 1e3, "launches": launches,
+                      "tflops": flops / sec / 1e12, "frac_of_bf16_peak": flops / sec / 1e12 / tf if dtype == BF16 else None,
+                      "phase_ms": ph}
+    # ---- decode: B sequences at context ctx, one token each per step ---------------------------------------------
+    out["decode"] = {}
+    for B in batches:
+        seqs = [eng.open() for _ in range(B)]
+        eng.step([(q, toks(ctx)) for q in seqs])
+        times = []
+        for i in range(warm + steps):
+            ent = [(q, toks(1)) for q in seqs]
+            flush()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            eng.step(ent)
+            dt = time.perf_counter() - t0
+            if i >= warm:
+                times.append(dt)
+        _, ph = eng.step([(q, toks(1)) for q in seqs], profile=True)
+        launches = eng.launches()
+        for q in seqs:
+            eng.close_seq(q)
+        sec = statistics.median(times)
+        # bytes a step must read: the active weights (distinct experts per token, an upper bound when tokens share
+        # experts) and the cached keys / values
+        W = shape.width
+        per_run_shared = (shape.n_in() * W + W * shape.heads * shape.vdim + 3 * shape.shared_ff * W) * es + shape.experts * W * 4
+        per_run_experts = min(B * shape.top, shape.experts) * 3 * shape.ff * W * es
+        kv = B * ctx * shape.kv_heads * (shape.dim + shape.vdim) * es
+        bytes_step = (per_run_shared + per_run_experts + kv) * shape.runs + shape.vocab * W * es
+        phase_bytes = {"in_proj": shape.n_in() * W * es * shape.runs, "out_proj": W * shape.heads * shape.vdim * es * shape.runs,
+                       "experts": per_run_experts * shape.runs, "shared": 3 * shape.shared_ff * W * es * shape.runs,
+                       "attention": kv * shape.runs, "head": shape.vocab * W * es}
+        out["decode"][str(B)] = {
+            "batch": B, "context": ctx, "tok_s": B / sec, "ms_per_step": sec * 1e3, "launches": launches,
+            "bytes_per_step": bytes_step, "frac_of_hbm_peak": bytes_step / sec / 1e9 / hbm, "phase_ms": ph,
+            "phase_frac_of_hbm_peak": {k: (v / (ph[k] * 1e-3) / 1e9 / hbm if ph[k] > 0 else None)
+                                       for k, v in phase_bytes.items()}}
+    eng.close()
+    return out
+
+
+def bench_llama(torch, shape, ctx, steps, warm, hbm, tf):
+    """The closest existing model at equal size: fp32 Llama through the single-sequence decoder."""
+    from . import Decoder, ModelShape, synth_weights
+    ls = ModelShape(f"llama-like-{shape.name}", shape.width, shape.top * shape.ff + shape.shared_ff, shape.runs,
+                    shape.heads, shape.kv_heads, shape.vocab, 2 * ctx)
+    w = synth_weights(ls, "cuda", 11)
+    dec = Decoder(ls, w)
+    dec.generate(1, 0, ctx)  # fill the cache
+    reps = []
+    for i in range(3):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        dec.generate(1, ctx, steps)
+        b.record()
+        torch.cuda.synchronize()
+        reps.append(a.elapsed_time(b) * 1e-3)
+    sec = statistics.median(reps) / steps
+    bytes_tok = ls.weight_bytes_per_token()
+    res = {"model": ls.name, "dtype": "fp32", "engine": dec.engine if hasattr(dec, "engine") else None,
+           "decode": {"batch": 1, "context": ctx, "tok_s": 1 / sec, "bytes_per_step": bytes_tok,
+                      "frac_of_hbm_peak": bytes_tok / sec / 1e9 / hbm}}
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, shape.vocab, (ctx,), generator=g).tolist()
+    try:
+        times = []
+        for i in range(warm + 3):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            dec.prefill_tf32(prompt, 0)
+            torch.cuda.synchronize()
+            if i >= warm:
+                times.append(time.perf_counter() - t0)
+        sec = statistics.median(times)
+        flops = 2 * (bytes_tok / 4 - shape.vocab * shape.width) * ctx + \
+            2 * ctx * ctx / 2 * 2 * (shape.width // shape.heads) * shape.heads * shape.runs
+        res["prefill"] = {"tokens": ctx, "tok_s": ctx / sec, "ms": sec * 1e3, "tflops": flops / sec / 1e12,
+                          "frac_of_tf32_peak": flops / sec / 1e12 / (tf / 2), "multiply": "tf32"}
+    except Exception as e:  # noqa: BLE001
+        res["prefill"] = {"unavailable": str(e)[:200]}
+    dec.close()
+    return res
+
+
+def bench_kernels(torch, shape, flush, hbm, tf):
+    """The like kernels of the two families at this size's projection shapes."""
+    import ctypes
+    from . import load_library
+    seq = load_seq_library()
+    core = load_library()
+    W, N, T = shape.width, shape.n_in(), 2048
+    res = {}
+    a16 = torch.randn(T, W, device="cuda").bfloat16()
+    w16 = torch.randn(N, W, device="cuda").bfloat16()
+    a32, w32 = a16.float(), w16.float()
+    out = torch.empty(T, N, device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    fl = 2.0 * T * W * N
+    ms = time_events(torch, lambda: seq.kllm_seq_gemm(BF16, p(a16), p(w16), p(out), T, W, N, None), flush)
+    res["block_product_bf16_tcgen05"] = {"shape": [T, W, N], "ms": ms, "tflops": fl / ms / 1e9,
+                                         "frac_of_bf16_peak": fl / ms / 1e9 / tf}
+    ms = time_events(torch, lambda: core.kllm_gemm_tf32(p(a32), p(w32), p(out), T, W, N, None), flush)
+    res["block_product_tf32_tcgen05_llama"] = {"shape": [T, W, N], "ms": ms, "tflops": fl / ms / 1e9,
+                                               "frac_of_tf32_peak": fl / ms / 1e9 / (tf / 2)}
+    ms = time_events(torch, lambda: seq.kllm_seq_gemm(F32, p(a32), p(w32), p(out), T, W, N, None), flush)
+    res["block_product_fp32_fma"] = {"shape": [T, W, N], "ms": ms, "tflops": fl / ms / 1e9}
+    # one row: the weights are streamed once
+    Nv = shape.vocab
+    wv16 = torch.randn(Nv, W, device="cuda").bfloat16()
+    wv32 = wv16.float()
+    o1 = torch.empty(Nv, device="cuda")
+    ms = time_events(torch, lambda: seq.kllm_seq_gemm(BF16, p(a16), p(wv16), p(o1), 1, W, Nv, None), flush)
+    res["row_product_bf16"] = {"shape": [1, W, Nv], "ms": ms, "frac_of_hbm_peak": Nv * W * 2 / ms / 1e6 / hbm}
+    ms = time_events(torch, lambda: seq.kllm_seq_gemm(F32, p(a32), p(wv32), p(o1), 1, W, Nv, None), flush)
+    res["row_product_fp32"] = {"shape": [1, W, Nv], "ms": ms, "frac_of_hbm_peak": Nv * W * 4 / ms / 1e6 / hbm}
+    ms = time_events(torch, lambda: core.kllm_gemv_f32(p(a32), p(wv32), p(o1), W, Nv, None), flush)
+    res["row_product_fp32_llama"] = {"shape": [1, W, Nv], "ms": ms, "frac_of_hbm_peak": Nv * W * 4 / ms / 1e6 / hbm}
+    return res
+
+
+def run(args, emit):
+    import torch
+    torch.cuda.set_device(0)
+    hbm, tf, src = peaks()
+    flush = Flusher(torch)
+    sizes = [s for s in (args.family_sizes.split(",") if args.family_sizes else ["s", "m"])]
+    steps, warm = max(3, min(args.steps, 16)), max(3, min(args.warmup, 8))
+    line = {"family": "fobolorn", "metric": "prefill_and_decode_tokens_per_s", "n_gpus": 1, "steps": steps, "warmup": warm,
+            "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+            "config": {"l2": "a 256 MiB buffer is written between timed steps", "timing": "wall clock around the blocking "
+                       "step call (token ids from host memory, greedy ids back to host memory); phases by CUDA events"},
+            "sizes": {}}
+    for name in sizes:
+        shape = SIZES[name]
+        ctx, prompt = (256, 512) if name == "debug" else (1024, 2048)
+        entry = {"shape": shape.__dict__ | {"runs": shape.runs}, "fobolorn": [], "closest": None, "kernels": None}
+        for dtype in (BF16, F32):
+            entry["fobolorn"].append(bench_engine(torch, shape, dtype, prompt, ctx, [1, 8], steps, warm, flush, hbm, tf))
+        entry["closest"] = bench_llama(torch, shape, ctx, max(steps, 32), warm, hbm, tf)
+        entry["kernels"] = bench_kernels(torch, shape, flush, hbm, tf)
+        line["sizes"][name] = entry
+    emit(line)

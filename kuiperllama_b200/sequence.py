@@ -1,0 +1,215 @@
+"""ctypes loader of the sequence-batch engine (include/kllm_seq.h) for bench.py and tests: torch tensors are the
+device memory, the engine and every kernel are the product library's.  Like the rest of this package it has no
+fallback: without libkllm_seq.so (or libkllm_b200.so, which carries the same symbols) it raises.
+
+`FobolornShape` + `synth_fobolorn()` build a random-weight model of the Fobolorn family directly in device memory
+(no model folder), for measurements at sizes that resemble a real model's layers.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from ctypes import POINTER, c_float, c_int32, c_void_p
+from dataclasses import dataclass
+
+F32, BF16 = 0, 1
+PHASES = ["norm", "in_proj", "qk_prepare", "attention", "out_proj", "router", "experts", "shared", "head"]
+
+
+class Norm(ctypes.Structure):
+    _fields_ = [("w", c_void_p), ("b", c_void_p)]
+
+
+class Attention(ctypes.Structure):
+    _fields_ = [("heads", c_int32), ("kv_heads", c_int32), ("dim", c_int32), ("vdim", c_int32), ("scale", c_float),
+                ("temp_coef", c_float), ("temp_every", c_int32), ("qk_norm", c_int32), ("gate", c_int32),
+                ("w_in", c_void_p), ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("w_out", c_void_p)]
+
+
+class Moe(ctypes.Structure):
+    _fields_ = [("experts", c_int32), ("top", c_int32), ("ff", c_int32), ("router_scale", c_float),
+                ("w_router", c_void_p), ("gate_up", c_void_p), ("down", c_void_p), ("shared_ff", c_int32),
+                ("shared_gate_up", c_void_p), ("shared_down", c_void_p), ("w_shared_gate", c_void_p)]
+
+
+class Layer(ctypes.Structure):
+    _fields_ = [("mixer_kind", c_int32), ("ff_kind", c_int32), ("pre_mixer", Norm), ("post_mixer", Norm),
+                ("pre_ff", Norm), ("post_ff", Norm), ("attn", Attention), ("moe", Moe)]
+
+
+class Desc(ctypes.Structure):
+    _fields_ = [("dtype", c_int32), ("width", c_int32), ("vocab", c_int32), ("norm_eps", c_float),
+                ("n_layers", c_int32), ("layers", POINTER(Layer)), ("n_runs", c_int32), ("run_layer", POINTER(c_int32)),
+                ("run_add", POINTER(c_int32)), ("run_vectors", c_void_p), ("embed", c_void_p), ("final_norm", Norm),
+                ("head", c_void_p), ("max_tokens", c_int32), ("max_seqs", c_int32), ("page_tokens", c_int32)]
+
+
+class SeqError(RuntimeError):
+    pass
+
+
+def load_seq_library():
+    from . import build
+    lib = ctypes.CDLL(str(build.build_seq()))
+    lib.kllm_seq_create.argtypes = [POINTER(Desc), c_void_p, POINTER(c_void_p)]
+    lib.kllm_seq_destroy.argtypes = [c_void_p]
+    lib.kllm_seq_destroy.restype = None
+    lib.kllm_seq_open.argtypes = [c_void_p, POINTER(c_int32)]
+    lib.kllm_seq_close.argtypes = [c_void_p, c_int32]
+    lib.kllm_seq_length.argtypes = [c_void_p, c_int32]
+    lib.kllm_seq_step.argtypes = [c_void_p, c_int32, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32), c_int32,
+                                  POINTER(c_int32), c_void_p, c_void_p]
+    lib.kllm_seq_profile.argtypes = [c_void_p, POINTER(c_float)]
+    lib.kllm_seq_last_launches.argtypes = [c_void_p]
+    lib.kllm_seq_gemm.argtypes = [c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]
+    lib.kllm_error_string.restype = ctypes.c_char_p
+    return lib
+
+
+def _check(lib, rc, what):
+    if rc != 0:
+        raise SeqError(f"{what}: {lib.kllm_error_string(rc).decode()} ({rc})")
+
+
+@dataclass
+class FobolornShape:
+    name: str
+    width: int
+    vocab: int
+    layers: int          # distinct layers
+    loop: tuple          # (start, stop, times)
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    experts: int
+    top: int
+    ff: int
+    shared_ff: int
+    temp: tuple = (0.5, 128)
+    eps: float = 1e-6
+
+    @property
+    def runs(self):
+        s, e, t = self.loop
+        return s + (e - s) * t + (self.layers - e)
+
+    def run_order(self):
+        s, e, t = self.loop
+        order = [(i, -1) for i in range(s)]
+        for p in range(t):
+            order += [(i, p if i == s else -1) for i in range(s, e)]
+        return order + [(i, -1) for i in range(e, self.layers)]
+
+    def n_in(self):
+        return self.heads * self.dim + self.kv_heads * (self.dim + self.vdim) + self.heads
+
+    def active_weight_elems_per_token(self):
+        """Matrix elements one decoded token of one sequence reads, per layer run and for the head."""
+        W = self.width
+        per_run = self.n_in() * W + W * self.heads * self.vdim + self.experts * W + \
+            self.top * 3 * self.ff * W + 3 * self.shared_ff * W
+        return per_run * self.runs + self.vocab * W
+
+    def flops_per_token(self):
+        return 2 * self.active_weight_elems_per_token()
+
+
+class SeqEngine:
+    """A random-weight Fobolorn model in device memory behind the engine's C-ABI."""
+
+    def __init__(self, shape: FobolornShape, dtype=BF16, max_tokens=4096, max_seqs=16, page=0, seed=1):
+        import torch
+        self.torch = torch
+        self.lib = load_seq_library()
+        self.shape, self.dtype = shape, dtype
+        td = torch.bfloat16 if dtype == BF16 else torch.float32
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        keep = self._keep = []
+        W = shape.width
+
+        def rnd(*dims, std, t=td):
+            x = (torch.randn(*dims, device="cuda", generator=g) * std).to(t).contiguous()
+            keep.append(x)
+            return x
+
+        def norm():
+            w = rnd(W, std=0.05, t=torch.float32)
+            w += 1
+            return Norm(w.data_ptr(), rnd(W, std=0.05, t=torch.float32).data_ptr())
+
+        layers = (Layer * shape.layers)()
+        for L in layers:
+            L.mixer_kind, L.ff_kind = 1, 1
+            L.pre_mixer, L.post_mixer, L.pre_ff, L.post_ff = norm(), norm(), norm(), norm()
+            a = L.attn
+            a.heads, a.kv_heads, a.dim, a.vdim = shape.heads, shape.kv_heads, shape.dim, shape.vdim
+            a.scale, a.temp_coef, a.temp_every, a.qk_norm, a.gate = shape.dim ** -0.5, shape.temp[0], shape.temp[1], 1, 1
+            a.w_in = rnd(shape.n_in(), W, std=W ** -0.5).data_ptr()
+            ones = rnd(shape.dim, std=0.05, t=torch.float32)
+            ones += 1
+            a.q_norm_w = a.k_norm_w = ones.data_ptr()
+            a.w_out = rnd(W, shape.heads * shape.vdim, std=(shape.heads * shape.vdim) ** -0.5).data_ptr()
+            m = L.moe
+            m.experts, m.top, m.ff, m.router_scale = shape.experts, shape.top, shape.ff, 1.0
+            m.w_router = rnd(shape.experts, W, std=W ** -0.5, t=torch.float32).data_ptr()
+            m.gate_up = rnd(shape.experts, 2 * shape.ff, W, std=W ** -0.5).data_ptr()
+            m.down = rnd(shape.experts, W, shape.ff, std=shape.ff ** -0.5).data_ptr()
+            m.shared_ff = shape.shared_ff
+            if shape.shared_ff:
+                m.shared_gate_up = rnd(2 * shape.shared_ff, W, std=W ** -0.5).data_ptr()
+                m.shared_down = rnd(W, shape.shared_ff, std=shape.shared_ff ** -0.5).data_ptr()
+                m.w_shared_gate = rnd(W, std=W ** -0.5, t=torch.float32).data_ptr()
+        order = shape.run_order()
+        run_layer = (c_int32 * len(order))(*[i for i, _ in order])
+        run_add = (c_int32 * len(order))(*[p for _, p in order])
+        d = Desc()
+        d.dtype, d.width, d.vocab, d.norm_eps = dtype, W, shape.vocab, shape.eps
+        d.n_layers, d.layers = shape.layers, layers
+        d.n_runs, d.run_layer, d.run_add = len(order), run_layer, run_add
+        d.run_vectors = rnd(max(1, shape.loop[2]), W, std=0.1, t=torch.float32).data_ptr()
+        d.embed = rnd(shape.vocab, W, std=1.0).data_ptr()
+        d.final_norm = norm()
+        d.head = rnd(shape.vocab, W, std=W ** -0.5).data_ptr()
+        d.max_tokens, d.max_seqs, d.page_tokens = max_tokens, max_seqs, page
+        self._desc = (d, layers, run_layer, run_add)
+        self.handle = c_void_p()
+        torch.cuda.synchronize()  # the engine runs on a stream of its own: the weights must be complete first
+        _check(self.lib, self.lib.kllm_seq_create(ctypes.byref(d), None, ctypes.byref(self.handle)), "kllm_seq_create")
+
+    def open(self):
+        s = c_int32(-1)
+        _check(self.lib, self.lib.kllm_seq_open(self.handle, ctypes.byref(s)), "kllm_seq_open")
+        return s.value
+
+    def close_seq(self, s):
+        _check(self.lib, self.lib.kllm_seq_close(self.handle, s), "kllm_seq_close")
+
+    def step(self, entries, want_last=True, profile=False):
+        """entries: [(seq, [tokens])].  Returns (greedy ids of the last row of every entry, phase ms or None).
+        Token ids go in from host memory and the ids come back to host memory: the call a server makes."""
+        seqs = (c_int32 * len(entries))(*[s for s, _ in entries])
+        counts = (c_int32 * len(entries))(*[len(t) for _, t in entries])
+        flat = [x for _, t in entries for x in t]
+        toks = (c_int32 * len(flat))(*flat)
+        want, at = [], 0
+        for _, t in entries:
+            at += len(t)
+            want.append(at - 1)
+        n_want = len(want) if want_last else 0
+        wantv = (c_int32 * max(1, len(want)))(*want)
+        out = (c_int32 * max(1, len(want)))()
+        ph = (c_float * len(PHASES))()
+        if profile:
+            self.lib.kllm_seq_profile(self.handle, ph)
+        _check(self.lib, self.lib.kllm_seq_step(self.handle, len(entries), seqs, counts, toks, n_want, wantv, None, out),
+               "kllm_seq_step")
+        return list(out)[:n_want], (dict(zip(PHASES, ph)) if profile else None)
+
+    def launches(self):
+        return self.lib.kllm_seq_last_launches(self.handle)
+
+    def close(self):
+        if self.handle:
+            self.lib.kllm_seq_destroy(self.handle)
+            self.handle = c_void_p()
