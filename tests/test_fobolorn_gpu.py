@@ -140,6 +140,26 @@ def test_long_decoding_crosses_tiles_and_temperature_steps(base):
     assert max(err) < TOL32, f"first bad position {int(np.argmax(np.array(err) >= TOL32))}"
 
 
+@pytest.mark.parametrize("sizes", [(2, 2, 2, 2), (5, 64, 3, 17), (33, 2, 70), (1, 99, 2)])
+def test_prompt_in_portions(base, sizes):
+    """A prompt fed in several steps of more than one token: every portion starts where the cache stands, so its rows
+    see the earlier portions' keys (and its own, causally).  A second request of another length rides along."""
+    cfg, w, d = base
+    t = toks(sum(sizes), cfg["vocab"], 81)
+    other = toks(2 * len(sizes) + 1, cfg["vocab"], 82)
+    ref, ref_o = ref_logits(cfg, w, t), ref_logits(cfg, w, other)
+    steps, at = [], 0
+    for i, n in enumerate(sizes):
+        o = other[2 * i:2 * i + 2] if i + 1 < len(sizes) else other[2 * i:]
+        steps.append({"entries": [{"id": "o", "tokens": o, "want": list(range(len(o)))},
+                                  {"id": "p", "tokens": t[at:at + n], "want": list(range(n))}]})
+        at += n
+    logits, _ = run_trace(d, steps, page=8, max_tokens=512)
+    got_o = np.concatenate([lg[:len(st["entries"][0]["tokens"])] for lg, st in zip(logits, steps)])
+    got_p = np.concatenate([lg[len(st["entries"][0]["tokens"]):] for lg, st in zip(logits, steps)])
+    assert rel_err(got_p, ref) < TOL32 and rel_err(got_o, ref_o) < TOL32
+
+
 # ---- batches --------------------------------------------------------------------------------------------------------
 def test_unequal_batch_equals_each_alone(base):
     cfg, w, d = base
