@@ -83,6 +83,13 @@ int launch_attention(int dtype, const AttnShape& a, const void* q, const float* 
                      const int32_t* ent_pos0, int max_count, int max_ctx, int splits, float* ws, void* out, int T,
                      const int32_t* tok_seq, const int32_t* tok_pos, cudaStream_t s);
 
+// Prompt steps in bf16 with head sizes up to 128 (multiples of 8): the same attention on the tensor cores (seq_attention_mma.cu).
+// With splits == 1 it writes `out` itself (gate applied); otherwise it leaves partial results in `ws` for the merge.
+bool attention_mma_usable(int dtype, const AttnShape& a, int max_count);
+int launch_attention_mma(const AttnShape& a, const void* q, const float* gates, const PagedKV& kv, int n_entries,
+                         const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
+                         const int32_t* ent_pos0, int max_count, int splits, float* ws, void* out, cudaStream_t s);
+
 // Router: z = Wr h (fp32), s = softmax(z), the `top` largest, weights s / (sum + 1e-20) * scale; shared-expert gate
 // sigmoid(w_sg . h) when w_sg is given.
 int launch_router(int dtype, const void* h, const float* w_router, const float* w_sg, int experts, int top,

@@ -764,6 +764,11 @@ int launch_attention(int dtype, const AttnShape& a, const void* q, const float* 
     return KLLM_E_UNSUPPORTED;
   const int C = (a.vdim + kAttnKeys - 1) / kAttnKeys;
   int rc = 0;
+  if (attention_mma_usable(dtype, a, max_count)) {
+    rc = launch_attention_mma(a, q, gates, kv, n_entries, ent_first, ent_count, ent_seq, ent_pos0, max_count, splits, ws,
+                              out, s);
+    if (rc || splits == 1) return rc;
+  } else {
 #define KLLM_ATTN_C(c)                                                                                              \
   KLLM_SEQ_DISPATCH(dtype, (rc = launch_attention_c<AT, c>(a, q, kv, n_entries, ent_first, ent_count, ent_seq, ent_pos0, \
                                                            max_count, splits, ws, s)))
@@ -774,6 +779,7 @@ int launch_attention(int dtype, const AttnShape& a, const void* q, const float* 
     default: KLLM_ATTN_C(4); break;
   }
 #undef KLLM_ATTN_C
+  }
   if (rc) return rc;
   KLLM_SEQ_DISPATCH(dtype, (attention_merge_kernel<AT><<<T * a.heads, 64, 0, s>>>(a.heads, a.vdim, splits, ws,
                                                                                  a.gate ? gates : nullptr,

@@ -226,6 +226,34 @@ def test_bfloat16_products(tmp_path):
     assert rel_err(np.concatenate(logits), ref) < TOL16
 
 
+@pytest.mark.parametrize("sizes", [((64, 128), (128, 64)), ((40, 24), (72, 104))])
+def test_bfloat16_prompt_attention_on_the_tensor_cores(tmp_path, sizes):
+    """Head sizes up to 128 in bf16 (multiples of 8; sizes below 64 or 128 run zero-padded): prompt steps take the tensor-core attention, single-token steps the split-key
+    kernel.  Both see the same bf16 inputs, so they agree far more tightly than either agrees with float64 -- a key
+    lost at a tile, page or portion edge would not.  Three query heads per key/value head (a 64-row tile cuts through a
+    token's heads), every expert chosen (no routing flips between the two runs), a ragged batch and a prompt in portions."""
+    cfg = make_config(width=128, vocab=90, layers=2, heads=6, kv_heads=2, dim=sizes[0][0], vdim=sizes[0][1], experts=3,
+                      top=3, ff=32, shared_ff=64, loop=(0, 1, 2), q_temp=(0.3, 40))
+    cfg["layers"][1]["mixer"].update(heads=2, kv_heads=2, dim=sizes[1][0], vdim=sizes[1][1])
+    w = make_weights(cfg, seed=91, sharp=2.0)
+    d = write_model(tmp_path, cfg, w)
+    reqs = {"a": toks(1, 90, 92), "b": toks(70, 90, 93), "c": toks(200, 90, 94), "p": toks(204, 90, 95)}
+    cuts = (50, 90, 64)
+    block = [{"entries": [{"id": k, "tokens": reqs[k], "want": list(range(len(reqs[k])))} for k in "abc"], "end": ["a", "b", "c"]}]
+    at = 0
+    for n in cuts:
+        block.append({"entries": [{"id": "p", "tokens": reqs["p"][at:at + n], "want": list(range(n))}]})
+        at += n
+    single = [{"entries": [{"id": k + "1", "tokens": [x], "want": [0]}]} for k in "abcp" for x in reqs[k]]
+    logits, _ = run_trace(d, block + single, dtype="bfloat16", page=16, max_tokens=1024)
+    got_block = np.concatenate(logits[:1 + len(cuts)])
+    got_single = np.concatenate(logits[1 + len(cuts):])
+    ref = np.concatenate([ref_logits(cfg, w, reqs[k]) for k in "abcp"])
+    assert rel_err(got_block, ref) < TOL16 and rel_err(got_single, ref) < TOL16
+    err = [rel_err(got_block[i:i + 1], got_single[i:i + 1]) for i in range(len(ref))]
+    assert max(err) < 1.5e-2, f"first bad row {int(np.argmax(np.array(err) >= 1.5e-2))}"
+
+
 def test_greedy_generation_through_the_scheduler(base):
     import subprocess
     from kuiperllama_b200 import build
