@@ -6,7 +6,8 @@
 // a token share every key tile), one warp 16 of them.
 //
 //   scores    S = Q K^T by mma.sync m16n8k16 (bf16 x bf16 -> fp32); scale, causal mask, running maximum and sum, and
-//             the exponentials are fp32 in registers (online softmax)
+//             the exponentials (ex2.approx on scores in units of log2, relative error about 2^-22) are fp32 in
+//             registers (online softmax); only tiles that touch the diagonal are masked
 //   weights   the fp32 weights p enter the second product as TWO bf16 terms, p = hi + lo (lo = p - hi rounded), so the
 //             product sees them to about 2^-17 instead of 2^-9: the values are bf16 already, the weights are not
 //   output    O += (hi + lo) V, fp32 accumulators; V fragments come transposed out of shared memory (ldmatrix.trans)
@@ -57,11 +58,22 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, u
 
 // (x, y) -> packed bf16 pairs hi and lo with x ~ hi.x + lo.x; the lower index sits in the low half
 __device__ __forceinline__ void split_pack(float x, float y, uint32_t& hi, uint32_t& lo) {
-  const __nv_bfloat16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
-  const __nv_bfloat16 xl = __float2bfloat16_rn(x - __bfloat162float(xh));
-  const __nv_bfloat16 yl = __float2bfloat16_rn(y - __bfloat162float(yh));
-  hi = static_cast<uint32_t>(__bfloat16_as_ushort(xh)) | (static_cast<uint32_t>(__bfloat16_as_ushort(yh)) << 16);
-  lo = static_cast<uint32_t>(__bfloat16_as_ushort(xl)) | (static_cast<uint32_t>(__bfloat16_as_ushort(yl)) << 16);
+  const __nv_bfloat162 h2 = __floats2bfloat162_rn(x, y);
+  hi = *reinterpret_cast<const uint32_t*>(&h2);
+  const float xh = __uint_as_float(hi << 16), yh = __uint_as_float(hi & 0xffff0000u);  // a bf16 is the top half of a float
+  const __nv_bfloat162 l2 = __floats2bfloat162_rn(x - xh, y - yh);
+  lo = *reinterpret_cast<const uint32_t*>(&l2);
+}
+
+__device__ __forceinline__ float exp2_approx(float x) {  // 2^x, relative error about 2^-22; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
 }
 
 __device__ __forceinline__ float quad_max(float v) {
@@ -74,7 +86,7 @@ __device__ __forceinline__ float quad_sum(float v) {
 }
 
 template <int DIM, int VDIM>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, (DIM + VDIM <= 128) ? 4 : 0)
 attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV kv, const int32_t* __restrict__ ent_first,
                      const int32_t* __restrict__ ent_count, const int32_t* __restrict__ ent_seq,
                      const int32_t* __restrict__ ent_pos0, int splits, float* __restrict__ ws,
@@ -109,6 +121,9 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
   const size_t thA = exA ? static_cast<size_t>(first + rA / rep) * a.heads + g * rep + rA % rep : 0;
   const size_t thB = exB ? static_cast<size_t>(first + rB / rep) * a.heads + g * rep + rB % rep : 0;
   const int warp_last = __reduce_max_sync(0xffffffffu, max(posA, posB));  // last position any row of the warp sees
+  // first position of the warp's rows (rows that do not exist count as -1: their tiles are always masked)
+  const int warp_first = __reduce_min_sync(0xffffffffu, min(posA, posB));
+  const float scale2 = a.scale * 1.4426950408889634f;  // scores are kept in units of log2: exp(x) = 2^(x log2 e)
 
   uint32_t qf[KS][4];
   {
@@ -135,13 +150,13 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
   const uint32_t vs_addr = static_cast<uint32_t>(__cvta_generic_to_shared(Vs));
 
   auto load_tile = [&](int tile, int stage) {
-    const int k0 = tile * kKeys;
-    for (int idx = tid; idx < kKeys * (KC + VC); idx += kThreads) {
-      const int j = idx / (KC + VC), c = idx % (KC + VC);
-      const int kj = k0 + j;
-      const bool valid = kj <= pmax;
-      size_t slot = 0;
-      if (valid) slot = static_cast<size_t>(table[kj / kv.page]) * kv.page + kj % kv.page;
+    // two threads per key: the page lookup is done once per key and thread
+    const int j = tid >> 1, kj = tile * kKeys + j;
+    const bool valid = kj <= pmax;
+    size_t slot = 0;
+    if (valid) slot = static_cast<size_t>(table[kj / kv.page]) * kv.page + kj % kv.page;
+#pragma unroll
+    for (int c = (tid & 1); c < KC + VC; c += 2) {
       if (c < KC) {
         const bool in = valid && c * 8 < dim;
         cp_async16(ks_addr + ((stage * kKeys + j) * LDK + c * 8) * 2,
@@ -167,38 +182,54 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
     __syncthreads();
     const int k0 = tile * kKeys;
     if (k0 <= warp_last) {  // otherwise no row of this warp sees a key of the tile
-      const __nv_bfloat16* Kt = Ks + stage * kKeys * LDK;
       float s[kKeys / 8][4];
 #pragma unroll
       for (int j = 0; j < kKeys / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      {
+        // one ldmatrix.x4 = the key fragments (b0, b1) of two k-steps for 8 keys: lane l addresses key row l % 8 of
+        // matrix l / 8 (matrices: dims +0, +8, +16, +24 of the same 8 keys)
+        const uint32_t kt = ks_addr + (stage * kKeys * LDK + (lane & 7) * LDK + (lane >> 3) * 8) * 2;
 #pragma unroll
-      for (int ks = 0; ks < KS; ++ks)
+        for (int ks = 0; ks < KS; ks += 2)
+#pragma unroll
+          for (int j = 0; j < kKeys / 8; ++j) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(kt + (j * 8 * LDK + ks * 16) * 2, b0, b1, b2, b3);
+            mma_bf16(s[j], qf[ks], b0, b1);
+            mma_bf16(s[j], qf[ks + 1], b2, b3);
+          }
+      }
+      float mxA = -INFINITY, mxB = -INFINITY;
+      if (k0 + kKeys - 1 <= warp_first) {  // every row of the warp sees the whole tile
 #pragma unroll
         for (int j = 0; j < kKeys / 8; ++j) {
-          const __nv_bfloat16* kp = Kt + (j * 8 + gq) * LDK + ks * 16 + t4 * 2;
-          mma_bf16(s[j], qf[ks], *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+          s[j][0] *= scale2, s[j][1] *= scale2, s[j][2] *= scale2, s[j][3] *= scale2;
+          mxA = fmaxf(mxA, fmaxf(s[j][0], s[j][1]));
+          mxB = fmaxf(mxB, fmaxf(s[j][2], s[j][3]));
         }
-      float mxA = -INFINITY, mxB = -INFINITY;
+      } else {
 #pragma unroll
-      for (int j = 0; j < kKeys / 8; ++j) {
-        const int kj = k0 + j * 8 + t4 * 2;
-        s[j][0] = kj <= posA ? s[j][0] * a.scale : -INFINITY;
-        s[j][1] = kj + 1 <= posA ? s[j][1] * a.scale : -INFINITY;
-        s[j][2] = kj <= posB ? s[j][2] * a.scale : -INFINITY;
-        s[j][3] = kj + 1 <= posB ? s[j][3] * a.scale : -INFINITY;
-        mxA = fmaxf(mxA, fmaxf(s[j][0], s[j][1]));
-        mxB = fmaxf(mxB, fmaxf(s[j][2], s[j][3]));
+        for (int j = 0; j < kKeys / 8; ++j) {
+          const int kj = k0 + j * 8 + t4 * 2;
+          s[j][0] = kj <= posA ? s[j][0] * scale2 : -INFINITY;
+          s[j][1] = kj + 1 <= posA ? s[j][1] * scale2 : -INFINITY;
+          s[j][2] = kj <= posB ? s[j][2] * scale2 : -INFINITY;
+          s[j][3] = kj + 1 <= posB ? s[j][3] * scale2 : -INFINITY;
+          mxA = fmaxf(mxA, fmaxf(s[j][0], s[j][1]));
+          mxB = fmaxf(mxB, fmaxf(s[j][2], s[j][3]));
+        }
       }
       const float nA = fmaxf(mA, quad_max(mxA)), nB = fmaxf(mB, quad_max(mxB));
-      const bool anyA = nA > -INFINITY, anyB = nB > -INFINITY;
-      const float alA = anyA ? expf(mA - nA) : 1.0f, alB = anyB ? expf(mB - nB) : 1.0f;
+      // a row that has seen nothing yet keeps max = -inf; subtracting 0 instead keeps 2^(-inf - 0) = 0 free of NaN
+      const float subA = nA > -INFINITY ? nA : 0.f, subB = nB > -INFINITY ? nB : 0.f;
+      const float alA = exp2_approx(mA - subA), alB = exp2_approx(mB - subB);
       float sumA = 0.f, sumB = 0.f;
 #pragma unroll
       for (int j = 0; j < kKeys / 8; ++j) {
-        s[j][0] = anyA ? expf(s[j][0] - nA) : 0.f;
-        s[j][1] = anyA ? expf(s[j][1] - nA) : 0.f;
-        s[j][2] = anyB ? expf(s[j][2] - nB) : 0.f;
-        s[j][3] = anyB ? expf(s[j][3] - nB) : 0.f;
+        s[j][0] = exp2_approx(s[j][0] - subA);
+        s[j][1] = exp2_approx(s[j][1] - subA);
+        s[j][2] = exp2_approx(s[j][2] - subB);
+        s[j][3] = exp2_approx(s[j][3] - subB);
         sumA += s[j][0] + s[j][1];
         sumB += s[j][2] + s[j][3];
       }
@@ -253,8 +284,9 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
   float* pa = ws + (thA * splits + split) * pstride;
   float* pb = ws + (thB * splits + split) * pstride;
   if (t4 == 0) {
-    if (exA) pa[0] = mA, pa[1] = lA;
-    if (exB) pb[0] = mB, pb[1] = lB;
+    constexpr float kLn2 = 0.6931471805599453f;  // the merge works with natural logarithms
+    if (exA) pa[0] = mA * kLn2, pa[1] = lA;
+    if (exB) pb[0] = mB * kLn2, pb[1] = lB;
   }
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) {

@@ -16,7 +16,8 @@
 //     gemm         output projection
 //     resid_norm   x += LN_post(y);  h = LN_pre_ff(x)
 //     router       fp32 logits, softmax, top-k, weights, shared-expert gate
-//     experts      few tokens: pair kernels (weights streamed once per chosen expert)
+//     experts      few tokens: pair kernels (weights streamed once per chosen expert; the shared expert rides along
+//                  as one more pair per token, so the three `shared` kernels below are not launched)
 //                  many tokens: pairs sorted by expert, two grouped products (SiLU-gate epilogue in the first)
 //     shared       gemm gate|up, silu_mul, gemm down
 //     resid_norm   x += LN_post_ff(routed + g_shared * shared)   [+ the next run's vector and pre-norm, fused]
@@ -477,9 +478,15 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       RC(launch_router(dtype, e->h.p, M.w_router, M.shared_ff > 0 ? M.w_shared_gate : nullptr, M.experts, M.top,
                        M.router_scale, top_idx, top_w, sgate, T, W, st));
       e->mark(KLLM_SEQ_PHASE_ROUTER);
+      bool shared_done = false;  // the shared expert went through the pair kernels: y already holds its part
       if (!grouped) {
-        RC(launch_expert_gate_up(dtype, e->h.p, M.gate_up, top_idx, e->inter.p, T, M.top, M.ff, W, st));
-        RC(launch_expert_down(dtype, e->inter.p, M.down, top_idx, top_w, y, T, M.top, M.ff, W, st));
+        SharedExpert sh{};
+        if (M.shared_ff > 0 && shared_expert_rides_along(M.top, M.ff, M.shared_ff)) {
+          sh = SharedExpert{M.shared_gate_up, M.shared_down, M.w_shared_gate ? sgate : nullptr, e->att.p, M.shared_ff};
+          shared_done = true;
+        }
+        RC(launch_expert_gate_up(dtype, e->h.p, M.gate_up, top_idx, e->inter.p, T, M.top, M.ff, W, sh, st));
+        RC(launch_expert_down(dtype, e->inter.p, M.down, top_idx, top_w, y, T, M.top, M.ff, W, sh, st));
       } else {
         const int n_pairs = T * M.top;
         const int cap = ((n_pairs + kGroupBlock - 1) / kGroupBlock + M.experts) * kGroupBlock;
@@ -511,7 +518,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
         RC(launch_combine_pairs(static_cast<const float*>(e->pairs_out.p), top_w, y, T, M.top, W, st));
       }
       e->mark(KLLM_SEQ_PHASE_EXPERTS);
-      const bool shared = M.shared_ff > 0;
+      const bool shared = M.shared_ff > 0 && !shared_done;
       if (shared) {
         RC(gemm(dtype, e->h.p, M.shared_gate_up, proj, T, W, 2 * M.shared_ff, st));
         RC(launch_silu_mul(dtype, proj, e->att.p, T, M.shared_ff, st));

@@ -98,10 +98,20 @@ int launch_router(int dtype, const void* h, const float* w_router, const float* 
 // Routed experts, one (token, chosen expert) pair at a time: inter[pair] = silu(Wg h) * (Wu h), then
 // y[t] = sum_k w_k * Wd_k inter[t, k].  gate_up: [experts][2*ff][width] (gate rows, then up rows); down:
 // [experts][width][ff].
+// A shared expert can ride along in both kernels (ff > 0): it is one more pair per token, chosen always, with its own
+// weights and inner size; y then holds routed + gate[t] * shared (gate NULL: 1).  Needs shared_expert_rides_along().
+struct SharedExpert {
+  const void* gate_up;  // [2*ff][width]
+  const void* down;     // [width][ff]
+  const float* gate;    // [T] or NULL
+  void* inter;          // [T, ff] workspace in the compute type
+  int ff;               // 0: no shared expert in these kernels
+};
+bool shared_expert_rides_along(int top, int ff, int shared_ff);
 int launch_expert_gate_up(int dtype, const void* h, const void* gate_up, const int32_t* top_idx, void* inter, int T,
-                          int top, int ff, int width, cudaStream_t s);
+                          int top, int ff, int width, const SharedExpert& sh, cudaStream_t s);
 int launch_expert_down(int dtype, const void* inter, const void* down, const int32_t* top_idx, const float* top_w,
-                       float* y, int T, int top, int ff, int width, cudaStream_t s);
+                       float* y, int T, int top, int ff, int width, const SharedExpert& sh, cudaStream_t s);
 
 // y[t] = sum_k w[t, k] * yp[t * top + k]   (fp32 [T * top, width] -> [T, width])
 int launch_combine_pairs(const float* yp, const float* top_w, float* y, int T, int top, int width, cudaStream_t s);

@@ -8,6 +8,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
+
 #include <cfloat>
 #include <cstdint>
 
@@ -544,33 +546,45 @@ __global__ void router_kernel(const AT* __restrict__ h, const float* __restrict_
 
 // ---- routed experts, pair by pair ----------------------------------------------------------------------------------
 constexpr int kPairRows = 16;  // expert rows per CTA
+// With a shared expert riding along (sh.ff > 0) the grid has T more "pairs": pair T * top + t is token t's pass
+// through the shared expert, whose inner activations go to sh.inter [T, sh.ff].
 template <typename AT>
 __global__ void expert_gate_up_kernel(const AT* __restrict__ h, const AT* __restrict__ gate_up,
-                                      const int32_t* __restrict__ top_idx, AT* __restrict__ inter, int top, int ff,
-                                      int width) {
+                                      const int32_t* __restrict__ top_idx, AT* __restrict__ inter, int T, int top, int ff,
+                                      int width, SharedExpert sh) {
   extern __shared__ float xs[];  // [width]
-  const int pair = blockIdx.x, t = pair / top, e = top_idx[pair];
+  const int pair = blockIdx.x;
+  const bool is_shared = pair >= T * top;
+  const int t = is_shared ? pair - T * top : pair / top;
+  const int rows = is_shared ? sh.ff : ff;
+  if (static_cast<int>(blockIdx.y) * kPairRows >= rows) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(h[static_cast<size_t>(t) * width + i]);
   __syncthreads();
-  const AT* wg = gate_up + static_cast<size_t>(e) * 2 * ff * width;
-  const AT* wu = wg + static_cast<size_t>(ff) * width;
-  const int f_end = min(ff, (blockIdx.y + 1) * kPairRows);
+  const AT* wg = is_shared ? static_cast<const AT*>(sh.gate_up)
+                           : gate_up + static_cast<size_t>(top_idx[pair]) * 2 * ff * width;
+  const AT* wu = wg + static_cast<size_t>(rows) * width;
+  AT* dst = is_shared ? static_cast<AT*>(sh.inter) + static_cast<size_t>(t) * sh.ff
+                      : inter + static_cast<size_t>(pair) * ff;
+  const int f_end = min(rows, (blockIdx.y + 1) * kPairRows);
   for (int f = blockIdx.y * kPairRows + warp; f < f_end; f += nw) {
     float gv, uv;
     warp_dot2(wg + static_cast<size_t>(f) * width, wu + static_cast<size_t>(f) * width, xs, width, lane, gv, uv);
-    if (lane == 0) inter[static_cast<size_t>(pair) * ff + f] = from_f<AT>(gv / (1.0f + expf(-gv)) * uv);
+    if (lane == 0) dst[f] = from_f<AT>(gv / (1.0f + expf(-gv)) * uv);
   }
 }
 
 template <typename AT>
 __global__ void expert_down_kernel(const AT* __restrict__ inter, const AT* __restrict__ down,
                                    const int32_t* __restrict__ top_idx, const float* __restrict__ top_w,
-                                   float* __restrict__ y, int top, int ff, int width) {
-  extern __shared__ float xs[];  // [top][ff]
+                                   float* __restrict__ y, int top, int ff, int width, SharedExpert sh) {
+  extern __shared__ float xs[];  // [top][ff], then [sh.ff]
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int i = threadIdx.x; i < top * ff; i += blockDim.x) xs[i] = to_f(inter[static_cast<size_t>(t) * top * ff + i]);
+  for (int i = threadIdx.x; i < sh.ff; i += blockDim.x)
+    xs[top * ff + i] = to_f(static_cast<const AT*>(sh.inter)[static_cast<size_t>(t) * sh.ff + i]);
+  const float shared_w = sh.ff > 0 && sh.gate ? sh.gate[t] : 1.0f;
   __syncthreads();
   const int n_end = min(width, (blockIdx.y + 1) * kPairRows);
   for (int n = blockIdx.y * kPairRows + warp; n < n_end; n += nw) {
@@ -580,6 +594,8 @@ __global__ void expert_down_kernel(const AT* __restrict__ inter, const AT* __res
       const AT* w = down + (static_cast<size_t>(e) * width + n) * ff;
       acc += top_w[static_cast<size_t>(t) * top + k] * warp_dot(w, xs + k * ff, ff, lane);
     }
+    if (sh.ff > 0)
+      acc += shared_w * warp_dot(static_cast<const AT*>(sh.down) + static_cast<size_t>(n) * sh.ff, xs + top * ff, sh.ff, lane);
     if (lane == 0) y[static_cast<size_t>(t) * width + n] = acc;
   }
 }
@@ -797,25 +813,30 @@ int launch_router(int dtype, const void* h, const float* w_router, const float* 
   return done();
 }
 
+bool shared_expert_rides_along(int top, int ff, int shared_ff) {
+  return (static_cast<size_t>(top) * ff + shared_ff) * sizeof(float) <= 48 * 1024;
+}
+
 int launch_expert_gate_up(int dtype, const void* h, const void* gate_up, const int32_t* top_idx, void* inter, int T,
-                          int top, int ff, int width, cudaStream_t s) {
+                          int top, int ff, int width, const SharedExpert& sh, cudaStream_t s) {
   const size_t smem = static_cast<size_t>(width) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
-  const dim3 grid(T * top, (ff + kPairRows - 1) / kPairRows);
+  const dim3 grid(T * top + (sh.ff > 0 ? T : 0), (std::max(ff, sh.ff) + kPairRows - 1) / kPairRows);
   KLLM_SEQ_DISPATCH(dtype, (expert_gate_up_kernel<AT><<<grid, 128, smem, s>>>(static_cast<const AT*>(h),
                                                                              static_cast<const AT*>(gate_up), top_idx,
-                                                                             static_cast<AT*>(inter), top, ff, width)));
+                                                                             static_cast<AT*>(inter), T, top, ff, width,
+                                                                             sh)));
   return done();
 }
 
 int launch_expert_down(int dtype, const void* inter, const void* down, const int32_t* top_idx, const float* top_w,
-                       float* y, int T, int top, int ff, int width, cudaStream_t s) {
-  const size_t smem = static_cast<size_t>(top) * ff * sizeof(float);
+                       float* y, int T, int top, int ff, int width, const SharedExpert& sh, cudaStream_t s) {
+  const size_t smem = (static_cast<size_t>(top) * ff + sh.ff) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
   const dim3 grid(T, (width + kPairRows - 1) / kPairRows);
   KLLM_SEQ_DISPATCH(dtype, (expert_down_kernel<AT><<<grid, 128, smem, s>>>(static_cast<const AT*>(inter),
                                                                           static_cast<const AT*>(down), top_idx, top_w,
-                                                                          y, top, ff, width)));
+                                                                          y, top, ff, width, sh)));
   return done();
 }
 
