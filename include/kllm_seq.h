@@ -118,7 +118,7 @@ int kllm_seq_trace_residual(kllm_seq_engine* eng, float* residual_host);
 #define KLLM_SEQ_PHASE_QK_PREPARE 2 /* head norms, temperature, cache scatter, gates */
 #define KLLM_SEQ_PHASE_ATTENTION 3  /* paged attention + merge of the key splits */
 #define KLLM_SEQ_PHASE_OUT_PROJ 4
-#define KLLM_SEQ_PHASE_ROUTER 5
+#define KLLM_SEQ_PHASE_ROUTER 5     /* residual + norms around the router and the router itself (one kernel) */
 #define KLLM_SEQ_PHASE_EXPERTS 6    /* routed experts */
 #define KLLM_SEQ_PHASE_SHARED 7     /* shared expert */
 #define KLLM_SEQ_PHASE_HEAD 8       /* final norm of the wanted rows, classifier, argmax, copies */

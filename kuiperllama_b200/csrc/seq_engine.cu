@@ -14,8 +14,8 @@
 //     qk_prepare   RMS norms, query temperature, scatter of k / v into the pages, sigmoid of the gates
 //     attention    causal, paged, keys split over CTAs; merge applies the gate
 //     gemm         output projection
-//     resid_norm   x += LN_post(y);  h = LN_pre_ff(x)
-//     router       fp32 logits, softmax, top-k, weights, shared-expert gate
+//     resid_norm   x += LN_post(y);  h = LN_pre_ff(x);  router on h: fp32 logits, softmax, top-k, weights,
+//                  shared-expert gate (same kernel: the row is still in shared memory)
 //     experts      few tokens: pair kernels (weights streamed once per chosen expert; the shared expert rides along
 //                  as one more pair per token, so the three `shared` kernels below are not launched)
 //                  many tokens: pairs sorted by expert, two grouped products (SiLU-gate epilogue in the first)
@@ -465,19 +465,18 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       e->mark(KLLM_SEQ_PHASE_NORM);
     } else {
       const kllm_seq_moe& M = L.moe;
-      {
-        ResidNormArgs a{};
-        a.x = x, a.y1 = y, a.post = nw(L.post_mixer), a.pre = nw(L.pre_ff), a.out = e->h.p, a.T = T, a.width = W;
-        a.dtype = dtype, a.eps = d.norm_eps;
-        RC(launch_resid_norm(a, st));
-        e->mark(KLLM_SEQ_PHASE_NORM);
-      }
       int32_t* top_idx = static_cast<int32_t*>(e->top_idx.p);
       float* top_w = static_cast<float*>(e->top_w.p);
       float* sgate = static_cast<float*>(e->sgate.p);
-      RC(launch_router(dtype, e->h.p, M.w_router, M.shared_ff > 0 ? M.w_shared_gate : nullptr, M.experts, M.top,
-                       M.router_scale, top_idx, top_w, sgate, T, W, st));
-      e->mark(KLLM_SEQ_PHASE_ROUTER);
+      {  // the norm kernel that writes the experts' input also routes its row
+        ResidNormArgs a{};
+        a.x = x, a.y1 = y, a.post = nw(L.post_mixer), a.pre = nw(L.pre_ff), a.out = e->h.p, a.T = T, a.width = W;
+        a.dtype = dtype, a.eps = d.norm_eps;
+        a.router = RouterArgs{M.w_router, M.shared_ff > 0 ? M.w_shared_gate : nullptr, M.experts, M.top, M.router_scale,
+                              top_idx, top_w, sgate};
+        RC(launch_resid_norm(a, st));
+        e->mark(KLLM_SEQ_PHASE_ROUTER);
+      }
       bool shared_done = false;  // the shared expert went through the pair kernels: y already holds its part
       if (!grouped) {
         SharedExpert sh{};

@@ -53,6 +53,18 @@ int launch_embed(int dtype, const void* table, const int32_t* tokens, float* x, 
 // x += LN(y1 + s2[t] * y2; post) (optional; y2 optional);  x += add (a [width] vector, optional);
 // out = LN(x; pre) in the compute type (optional) -- in this order.  `rows` (optional) gathers: row i reads x[rows[i]], and x is then
 // left untouched (only `out` is written).
+// Router of a mixture of experts for the rows of `out` (optional, w_router != NULL; needs `pre`): logits z = Wr h in
+// fp32 on the row just written, s = softmax(z), the `top` largest, weights s / (sum + 1e-20) * scale; shared-expert gate
+// sigmoid(w_sg . h) when w_sg is given.
+struct RouterArgs {
+  const float* w_router;  // [experts][width]
+  const float* w_sg;      // [width] or NULL
+  int experts, top;
+  float scale;
+  int32_t* top_idx;       // [T, top]
+  float* top_w;           // [T, top]
+  float* sgate;           // [T]
+};
 struct ResidNormArgs {
   float* x;
   const float* add;
@@ -65,6 +77,7 @@ struct ResidNormArgs {
   const int32_t* rows;
   int T, width, dtype;
   float eps;
+  RouterArgs router;
 };
 int launch_resid_norm(const ResidNormArgs& a, cudaStream_t s);
 

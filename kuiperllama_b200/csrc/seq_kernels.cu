@@ -140,11 +140,78 @@ __global__ void embed_kernel(const AT* __restrict__ table, const int32_t* __rest
   for (int i = threadIdx.x; i < width; i += blockDim.x) x[static_cast<size_t>(t) * width + i] = to_f(row[i]);
 }
 
+// ---- router ---------------------------------------------------------------------------------------------------------
+// The warps of a CTA share the experts' logits of ONE token whose row `xs` is in shared memory in fp32 (a warp per
+// expert row, fp32 weights); warp 0 then does the softmax over all experts and picks the top-k.  `z`: [experts] shared.
+__device__ void route_token(const RouterArgs& r, const float* xs, float* z, int t, int width) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int experts = r.experts, top = r.top;
+  for (int e = warp; e < experts + (r.w_sg ? 1 : 0); e += nw) {
+    const float* w = e < experts ? r.w_router + static_cast<size_t>(e) * width : r.w_sg;
+    const float acc = warp_dot<float>(w, xs, width, lane);
+    if (lane == 0) {
+      if (e < experts) z[e] = acc;
+      else r.sgate[t] = 1.0f / (1.0f + expf(-acc));
+    }
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float mx = -INFINITY;
+  for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < experts; e += 32) {
+    const float p = expf(z[e] - mx);
+    z[e] = p;
+    sum += p;
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < experts; e += 32) z[e] = z[e] / sum;
+  __syncwarp();
+  float chosen_sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -1.0f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = z[e];
+      if (v > best) best = v, bi = e;  // ascending e: the lowest index wins a tie inside the lane
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(kAll, best, o);
+      const int oi = __shfl_xor_sync(kAll, bi, o);
+      if (ob > best || (ob == best && oi < bi)) best = ob, bi = oi;
+    }
+    chosen_sum += best;
+    if (lane == 0) {
+      r.top_idx[static_cast<size_t>(t) * top + k] = bi;
+      r.top_w[static_cast<size_t>(t) * top + k] = best;
+      z[bi] = -2.0f;  // softmax outputs are >= 0: never chosen again
+    }
+    __syncwarp();
+  }
+  const float inv = r.scale / (chosen_sum + 1e-20f);
+  for (int k = lane; k < top; k += 32) r.top_w[static_cast<size_t>(t) * top + k] *= inv;
+}
+
+template <typename AT>
+__global__ void router_kernel(const AT* __restrict__ h, RouterArgs r, int width) {
+  extern __shared__ float sm[];  // [experts] logits, then [width] the token's row in fp32
+  float* z = sm;
+  float* xs = sm + r.experts;
+  const int t = blockIdx.x;
+  const AT* x = h + static_cast<size_t>(t) * width;
+  for (int k = threadIdx.x; k < width; k += blockDim.x) xs[k] = to_f(x[k]);
+  __syncthreads();
+  route_token(r, xs, z, t, width);
+}
+
 // ---- residual + layer norms ---------------------------------------------------------------------------------------
 // Layer norm as the model family defines it: (v - mean) / sqrt(var + eps) * w + b, var = mean of squared deviations.
 template <typename AT>
 __global__ void resid_norm_kernel(ResidNormArgs a) {
-  extern __shared__ float buf[];  // [width]
+  extern __shared__ float buf[];  // [width], then [experts] when the kernel also routes
   __shared__ float red[33];
   const int W = a.width;
   const int r = blockIdx.x;
@@ -198,8 +265,15 @@ __global__ void resid_norm_kernel(ResidNormArgs a) {
   const float var = block_sum(q, red) * inv_w;
   const float rstd = 1.0f / sqrtf(var + a.eps);
   AT* out = static_cast<AT*>(a.out) + dst;
-  for (int i = threadIdx.x; i < W; i += blockDim.x)
-    out[i] = from_f<AT>((buf[i] - mean) * rstd * a.pre.w[i] + (a.pre.b ? a.pre.b[i] : 0.f));
+  const bool route = a.router.w_router != nullptr;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const AT o = from_f<AT>((buf[i] - mean) * rstd * a.pre.w[i] + (a.pre.b ? a.pre.b[i] : 0.f));
+    out[i] = o;
+    if (route) buf[i] = to_f(o);  // the router reads what the experts read: the row in the compute type
+  }
+  if (!route) return;
+  __syncthreads();
+  route_token(a.router, buf, buf + W, r, W);
 }
 
 // ---- query / key preparation ----------------------------------------------------------------------------------------
@@ -322,20 +396,37 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
     if (vec_tiles) {  // 16-byte loads: a key's row is dim / V chunks
       constexpr int V = VecOf<AT>::N;
       const int kc = a.dim / V, vc = a.vdim / V;
-      for (int idx = tid; idx < kAttnKeys * (kc + vc); idx += kAttnThreads) {
-        const int j = idx / (kc + vc), c = idx % (kc + vc);
-        const int kj = k0 + j;
-        float f[V];
+      // four chunks per thread are in flight before the first is stored: a split of a decode step has one or two
+      // tiles, so the tile's load latency is paid once, not once per chunk
+      constexpr int U = 4;
+      const int total = kAttnKeys * (kc + vc);
+      for (int base = tid; base < total; base += kAttnThreads * U) {
+        float f[U][V];
 #pragma unroll
-        for (int i = 0; i < V; ++i) f[i] = 0.f;
-        if (kj <= pmax) {
-          const size_t slot = static_cast<size_t>(table[kj / kv.page]) * kv.page + kj % kv.page;
-          if (c < kc) VecOf<AT>::load(kbase + (slot * a.kv_heads + g) * a.dim + c * V, f);
-          else VecOf<AT>::load(vbase + (slot * a.kv_heads + g) * a.vdim + (c - kc) * V, f);
+        for (int u = 0; u < U; ++u) {
+          const int idx = base + u * kAttnThreads;
+#pragma unroll
+          for (int i = 0; i < V; ++i) f[u][i] = 0.f;
+          if (idx < total) {
+            const int j = idx / (kc + vc), c = idx % (kc + vc);
+            const int kj = k0 + j;
+            if (kj <= pmax) {
+              const size_t slot = static_cast<size_t>(table[kj / kv.page]) * kv.page + kj % kv.page;
+              if (c < kc) VecOf<AT>::load(kbase + (slot * a.kv_heads + g) * a.dim + c * V, f[u]);
+              else VecOf<AT>::load(vbase + (slot * a.kv_heads + g) * a.vdim + (c - kc) * V, f[u]);
+            }
+          }
         }
-        float* dst = c < kc ? Ks + j * dk + c * V : Vs + j * a.vdim + (c - kc) * V;
 #pragma unroll
-        for (int i = 0; i < V; ++i) dst[i] = f[i];
+        for (int u = 0; u < U; ++u) {
+          const int idx = base + u * kAttnThreads;
+          if (idx < total) {
+            const int j = idx / (kc + vc), c = idx % (kc + vc);
+            float* dst = c < kc ? Ks + j * dk + c * V : Vs + j * a.vdim + (c - kc) * V;
+#pragma unroll
+            for (int i = 0; i < V; ++i) dst[i] = f[u][i];
+          }
+        }
       }
       if (dk > a.dim)
         for (int idx = tid; idx < kAttnKeys * (dk - a.dim); idx += kAttnThreads)
@@ -477,71 +568,6 @@ __global__ void attention_merge_kernel(int heads, int vdim, int splits, const fl
     }
     out[th * vdim + d] = from_f<AT>(o / L * gate);
   }
-}
-
-// ---- router ---------------------------------------------------------------------------------------------------------
-// One CTA per token: the warps share the experts' logits (a warp per expert row, fp32 weights), then warp 0 does the
-// softmax over all experts and picks the top-k.
-template <typename AT>
-__global__ void router_kernel(const AT* __restrict__ h, const float* __restrict__ w_router,
-                              const float* __restrict__ w_sg, int experts, int top, float scale,
-                              int32_t* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ sgate, int T,
-                              int width) {
-  extern __shared__ float sm[];  // [experts] logits, then [width] the token's row in fp32
-  float* z = sm;
-  float* xs = sm + experts;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const int t = blockIdx.x;
-  const AT* x = h + static_cast<size_t>(t) * width;
-  for (int k = threadIdx.x; k < width; k += blockDim.x) xs[k] = to_f(x[k]);
-  __syncthreads();
-  for (int e = warp; e < experts + (w_sg ? 1 : 0); e += nw) {
-    const float* w = e < experts ? w_router + static_cast<size_t>(e) * width : w_sg;
-    const float acc = warp_dot<float>(w, xs, width, lane);
-    if (lane == 0) {
-      if (e < experts) z[e] = acc;
-      else sgate[t] = 1.0f / (1.0f + expf(-acc));
-    }
-  }
-  __syncthreads();
-  if (warp != 0) return;
-  float mx = -INFINITY;
-  for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < experts; e += 32) {
-    const float p = expf(z[e] - mx);
-    z[e] = p;
-    sum += p;
-  }
-  sum = warp_sum(sum);
-  __syncwarp();
-  for (int e = lane; e < experts; e += 32) z[e] = z[e] / sum;
-  __syncwarp();
-  float chosen_sum = 0.f;
-  for (int k = 0; k < top; ++k) {
-    float best = -1.0f;
-    int bi = 0x7fffffff;
-    for (int e = lane; e < experts; e += 32) {
-      const float v = z[e];
-      if (v > best) best = v, bi = e;  // ascending e: the lowest index wins a tie inside the lane
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(kAll, best, o);
-      const int oi = __shfl_xor_sync(kAll, bi, o);
-      if (ob > best || (ob == best && oi < bi)) best = ob, bi = oi;
-    }
-    chosen_sum += best;
-    if (lane == 0) {
-      top_idx[static_cast<size_t>(t) * top + k] = bi;
-      top_w[static_cast<size_t>(t) * top + k] = best;
-      z[bi] = -2.0f;  // softmax outputs are >= 0: never chosen again
-    }
-    __syncwarp();
-  }
-  const float inv = scale / (chosen_sum + 1e-20f);
-  for (int k = lane; k < top; k += 32) top_w[static_cast<size_t>(t) * top + k] *= inv;
 }
 
 // ---- routed experts, pair by pair ----------------------------------------------------------------------------------
@@ -715,8 +741,10 @@ int launch_embed(int dtype, const void* table, const int32_t* tokens, float* x, 
 }
 
 int launch_resid_norm(const ResidNormArgs& a, cudaStream_t s) {
-  const size_t smem = static_cast<size_t>(a.width) * sizeof(float);
+  const size_t smem = (static_cast<size_t>(a.width) + (a.router.w_router ? a.router.experts : 0)) * sizeof(float);
   if (smem > 200 * 1024) return KLLM_E_UNSUPPORTED;
+  if (a.router.w_router && (a.router.top > a.router.experts || a.router.experts <= 0 || a.router.top <= 0 || !a.pre.w))
+    return KLLM_E_INVALID;
   const int threads = a.width >= 1024 ? 256 : 128;
   if (smem > 48 * 1024) {
     KLLM_SEQ_DISPATCH(a.dtype, (cudaFuncSetAttribute(resid_norm_kernel<AT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -808,8 +836,8 @@ int launch_router(int dtype, const void* h, const float* w_router, const float* 
   if (top > experts || experts <= 0 || top <= 0) return KLLM_E_INVALID;
   const size_t smem = (static_cast<size_t>(experts) + width) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
-  KLLM_SEQ_DISPATCH(dtype, (router_kernel<AT><<<T, 256, smem, s>>>(static_cast<const AT*>(h), w_router, w_sg, experts, top,
-                                                                  scale, top_idx, top_w, sgate, T, width)));
+  const RouterArgs r{w_router, w_sg, experts, top, scale, top_idx, top_w, sgate};
+  KLLM_SEQ_DISPATCH(dtype, (router_kernel<AT><<<T, 256, smem, s>>>(static_cast<const AT*>(h), r, width)));
   return done();
 }
 
