@@ -49,6 +49,7 @@ namespace {
 constexpr int kDefaultPage = 16;
 constexpr int kGroupedMinTokens = 64;  // steps with at least this many tokens run the routed experts as grouped products
 constexpr int kGroupBlock = 64;
+constexpr int kSharedRideTokens = 4;   // steps of at most this many tokens run the shared expert inside the pair kernels
 
 inline NormW nw(const kllm_seq_norm& n) { return NormW{n.w, n.b}; }
 inline size_t elt(int dtype) { return dtype == KLLM_SEQ_BF16 ? 2 : 4; }
@@ -480,7 +481,8 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       bool shared_done = false;  // the shared expert went through the pair kernels: y already holds its part
       if (!grouped) {
         SharedExpert sh{};
-        if (M.shared_ff > 0 && shared_expert_rides_along(M.top, M.ff, M.shared_ff)) {
+        // every pair streams its expert's weights once: beyond a few tokens the shared expert is cheaper as a product
+        if (M.shared_ff > 0 && T <= kSharedRideTokens && shared_expert_rides_along(M.top, M.ff, M.shared_ff)) {
           sh = SharedExpert{M.shared_gate_up, M.shared_down, M.w_shared_gate ? sgate : nullptr, e->att.p, M.shared_ff};
           shared_done = true;
         }

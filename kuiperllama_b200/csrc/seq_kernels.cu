@@ -571,7 +571,9 @@ __global__ void attention_merge_kernel(int heads, int vdim, int splits, const fl
 }
 
 // ---- routed experts, pair by pair ----------------------------------------------------------------------------------
-constexpr int kPairRows = 16;  // expert rows per CTA
+// Expert rows per CTA: 16 (four per warp) when a step has many pairs; 4 (one per warp) when it has few, so that a decode
+// step spreads over every SM and a warp waits for memory once or twice instead of eight times.
+__host__ __device__ inline int pair_rows(int pairs) { return pairs <= 32 ? 4 : 16; }
 // With a shared expert riding along (sh.ff > 0) the grid has T more "pairs": pair T * top + t is token t's pass
 // through the shared expert, whose inner activations go to sh.inter [T, sh.ff].
 template <typename AT>
@@ -583,6 +585,7 @@ __global__ void expert_gate_up_kernel(const AT* __restrict__ h, const AT* __rest
   const bool is_shared = pair >= T * top;
   const int t = is_shared ? pair - T * top : pair / top;
   const int rows = is_shared ? sh.ff : ff;
+  const int kPairRows = pair_rows(T * top);
   if (static_cast<int>(blockIdx.y) * kPairRows >= rows) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(h[static_cast<size_t>(t) * width + i]);
@@ -612,6 +615,7 @@ __global__ void expert_down_kernel(const AT* __restrict__ inter, const AT* __res
     xs[top * ff + i] = to_f(static_cast<const AT*>(sh.inter)[static_cast<size_t>(t) * sh.ff + i]);
   const float shared_w = sh.ff > 0 && sh.gate ? sh.gate[t] : 1.0f;
   __syncthreads();
+  const int kPairRows = pair_rows(static_cast<int>(gridDim.x) * top);
   const int n_end = min(width, (blockIdx.y + 1) * kPairRows);
   for (int n = blockIdx.y * kPairRows + warp; n < n_end; n += nw) {
     float acc = 0.f;
@@ -757,7 +761,9 @@ int launch_resid_norm(const ResidNormArgs& a, cudaStream_t s) {
 int launch_qk_prepare(int dtype, const AttnShape& a, const float* qkvg, const float* qnorm_w, const float* knorm_w,
                       float eps, const int32_t* tok_seq, const int32_t* tok_pos, void* q, float* gates,
                       const PagedKV& kv, int T, cudaStream_t s) {
-  KLLM_SEQ_DISPATCH(dtype, (qk_prepare_kernel<AT><<<T, 128, 0, s>>>(a, qkvg, qnorm_w, knorm_w, eps, tok_seq, tok_pos,
+  // a warp per head: few tokens get as many warps as there are query and key heads
+  const int threads = T <= 64 ? std::min(1024, 32 * std::max(4, a.heads + a.kv_heads)) : 128;
+  KLLM_SEQ_DISPATCH(dtype, (qk_prepare_kernel<AT><<<T, threads, 0, s>>>(a, qkvg, qnorm_w, knorm_w, eps, tok_seq, tok_pos,
                                                                     static_cast<AT*>(q), gates, kv)));
   return done();
 }
@@ -849,6 +855,7 @@ int launch_expert_gate_up(int dtype, const void* h, const void* gate_up, const i
                           int top, int ff, int width, const SharedExpert& sh, cudaStream_t s) {
   const size_t smem = static_cast<size_t>(width) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
+  const int kPairRows = pair_rows(T * top);
   const dim3 grid(T * top + (sh.ff > 0 ? T : 0), (std::max(ff, sh.ff) + kPairRows - 1) / kPairRows);
   KLLM_SEQ_DISPATCH(dtype, (expert_gate_up_kernel<AT><<<grid, 128, smem, s>>>(static_cast<const AT*>(h),
                                                                              static_cast<const AT*>(gate_up), top_idx,
@@ -861,6 +868,7 @@ int launch_expert_down(int dtype, const void* inter, const void* down, const int
                        float* y, int T, int top, int ff, int width, const SharedExpert& sh, cudaStream_t s) {
   const size_t smem = (static_cast<size_t>(top) * ff + sh.ff) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
+  const int kPairRows = pair_rows(T * top);
   const dim3 grid(T, (width + kPairRows - 1) / kPairRows);
   KLLM_SEQ_DISPATCH(dtype, (expert_down_kernel<AT><<<grid, 128, smem, s>>>(static_cast<const AT*>(inter),
                                                                           static_cast<const AT*>(down), top_idx, top_w,
