@@ -359,7 +359,8 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
   float* al_s = l_s + kAttnRows;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int i = tid; i < kAttnRows * dq; i += kAttnThreads) {
+  // SPARSE: only the rows that exist are filled (and read)
+  for (int i = tid; i < (SPARSE ? rows_here : kAttnRows) * dq; i += kAttnThreads) {
     const int r = i / dq, d = i % dq;
     float v = 0.f;
     if (r < rows_here && d < a.dim) {
@@ -386,9 +387,11 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
   const AT* vbase = static_cast<const AT*>(kv.v);
   const int32_t* table = kv.table + static_cast<size_t>(seq) * kv.table_stride;
   const bool vec_tiles = SPARSE && (a.dim % VecOf<AT>::N) == 0 && (a.vdim % VecOf<AT>::N) == 0;
-  // rows of this thread that exist (a decode step fills only heads / kv_heads rows of the tile)
-  const int my_rows = max(0, min(static_cast<int>(kAttnRows / (kAttnThreads / kAttnKeys)),
-                                 rows_here - (tid / kAttnKeys) * (kAttnRows / (kAttnThreads / kAttnKeys))));
+  // Rows of this thread: thread group rg takes rows rg * rpt .. rg * rpt + my_rows - 1.  A full tile gives each of the
+  // two groups 16 rows; a SPARSE tile (a decode step fills only heads / kv_heads rows) splits the rows that exist
+  // between the groups, so both halves of the CTA work.
+  const int rpt = SPARSE ? (rows_here + 1) / 2 : RPT;
+  const int my_rows = max(0, min(rpt, rows_here - rg * rpt));
 
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
     const int k0 = tile * kAttnKeys;
@@ -459,7 +462,7 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
           if (SPARSE && i >= my_rows) break;
-          const float4 qv = *reinterpret_cast<const float4*>(Qs + (rg * RPT + i) * dq + d);
+          const float4 qv = *reinterpret_cast<const float4*>(Qs + (rg * rpt + i) * dq + d);
           sc[i] = fmaf(qv.x, k0v, sc[i]);
           sc[i] = fmaf(qv.y, k1v, sc[i]);
           sc[i] = fmaf(qv.z, k2v, sc[i]);
@@ -469,7 +472,8 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
       const int kj = k0 + key;
 #pragma unroll
       for (int i = 0; i < RPT; ++i) {
-        const int r = rg * RPT + i;
+        if (SPARSE && i >= my_rows) break;  // the softmax below reads only rows that exist
+        const int r = rg * rpt + i;
         const bool visible = r < rows_here && kj <= pos0 + (r0 + r) / rep;
         Ss[r * kAttnKeys + key] = visible ? sc[i] : -INFINITY;
       }
@@ -498,7 +502,7 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
       if (SPARSE && i >= my_rows) break;
-      const float al = al_s[rg * RPT + i];
+      const float al = al_s[rg * rpt + i];
 #pragma unroll
       for (int c = 0; c < C; ++c) acc[i][c] *= al;
     }
@@ -514,7 +518,7 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
 #pragma unroll
       for (int i = 0; i < RPT; ++i) {
         if (SPARSE && i >= my_rows) break;
-        const float4 p = *reinterpret_cast<const float4*>(Ss + (rg * RPT + i) * kAttnKeys + j);
+        const float4 p = *reinterpret_cast<const float4*>(Ss + (rg * rpt + i) * kAttnKeys + j);
 #pragma unroll
         for (int c = 0; c < C; ++c) {
           acc[i][c] = fmaf(p.x, vv[0][c], acc[i][c]);
@@ -529,8 +533,8 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
   const int pstride = a.vdim + 2;
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
-    const int r = rg * RPT + i;
-    if (r >= rows_here) continue;
+    const int r = rg * rpt + i;
+    if (i >= my_rows || r >= rows_here) continue;
     const int rr = r0 + r;
     const int t = first + rr / rep, h = g * rep + rr % rep;
     float* p = ws + ((static_cast<size_t>(t) * a.heads + h) * splits + split) * pstride;

@@ -139,23 +139,40 @@ def bench_llama(torch, shape, ctx, steps, warm, hbm, tf):
     from . import Decoder, ModelShape, synth_weights
     ls = ModelShape(f"llama-like-{shape.name}", shape.width, shape.top * shape.ff + shape.shared_ff, shape.runs,
                     shape.heads, shape.kv_heads, shape.vocab, 2 * ctx)
+    import os
     w = synth_weights(ls, "cuda", 11)
-    dec = Decoder(ls, w)
-    dec.generate(1, 0, ctx)  # fill the cache
-    reps = []
-    for i in range(3):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        a.record()
-        dec.generate(1, ctx, steps)
-        b.record()
-        torch.cuda.synchronize()
-        reps.append(a.elapsed_time(b) * 1e-3)
-    sec = statistics.median(reps) / steps
     bytes_tok = ls.weight_bytes_per_token()
-    res = {"model": ls.name, "dtype": "fp32", "engine": dec.engine if hasattr(dec, "engine") else None,
-           "decode": {"batch": 1, "context": ctx, "tok_s": 1 / sec, "bytes_per_step": bytes_tok,
-                      "frac_of_hbm_peak": bytes_tok / sec / 1e9 / hbm}}
+
+    def decode_rate(dec):
+        dec.generate(1, 0, ctx)  # fill the cache
+        reps = []
+        for i in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            dec.generate(1, ctx, steps)
+            b.record()
+            torch.cuda.synchronize()
+            reps.append(a.elapsed_time(b) * 1e-3)
+        sec = statistics.median(reps) / steps
+        return {"batch": 1, "context": ctx, "engine": dec.engine, "tok_s": 1 / sec, "ms_per_step": sec * 1e3,
+                "bytes_per_step": bytes_tok, "frac_of_hbm_peak": bytes_tok / sec / 1e9 / hbm}
+    # the family's other decode engine, a CUDA graph of one fused kernel per phase: the like of the batched engine's
+    # decode step (a graph of small kernels); the persistent kernel is the default
+    old_env = os.environ.get("KLLM_ENGINE")
+    os.environ["KLLM_ENGINE"] = "graph"
+    try:
+        dec = Decoder(ls, w)
+        graph_rate = decode_rate(dec)
+        dec.close()
+    finally:
+        if old_env is None:
+            del os.environ["KLLM_ENGINE"]
+        else:
+            os.environ["KLLM_ENGINE"] = old_env
+    dec = Decoder(ls, w)
+    res = {"model": ls.name, "dtype": "fp32", "engine": dec.engine, "decode": decode_rate(dec),
+           "decode_graph_engine": graph_rate}
     g = torch.Generator().manual_seed(2)
     prompt = torch.randint(0, shape.vocab, (ctx,), generator=g).tolist()
     try:
