@@ -95,12 +95,14 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
   constexpr int KS = DIM / 16;                  // k-steps of Q K^T
   constexpr int NB = VDIM / 8;                  // 8-column blocks of the output
   constexpr int KC = DIM / 8, VC = VDIM / 8;    // 16-byte chunks per key / value row
-  const int e = blockIdx.y / a.kv_heads, g = blockIdx.y % a.kv_heads, split = blockIdx.z;
+  // grid: x = (entry, key/value head), y = row tile, z = split.  CTAs are handed out in x-fastest order, so the tiles
+  // of equal weight (the same rows of every head) start together, heaviest first
+  const int e = blockIdx.x / a.kv_heads, g = blockIdx.x % a.kv_heads, split = blockIdx.z;
   const int rep = a.heads / a.kv_heads;
   const int dim = a.dim, vdim = a.vdim;  // <= DIM, VDIM; multiples of 8
   const int count = ent_count[e], first = ent_first[e], seq = ent_seq[e], pos0 = ent_pos0[e];
   const int n_rows = count * rep;
-  const int r0 = (gridDim.x - 1 - blockIdx.x) * kRows;  // the tiles with the most keys start first
+  const int r0 = (gridDim.y - 1 - blockIdx.y) * kRows;  // the tiles with the most keys start first
   if (r0 >= n_rows) return;
   const int rows_here = min(kRows, n_rows - r0);
   const int pmax = pos0 + (r0 + rows_here - 1) / rep;  // last position any row of the tile sees
@@ -310,7 +312,8 @@ int launch_mma(const AttnShape& a, const void* q, const float* gates, const Page
     configured = true;
   }
   const int rep = a.heads / a.kv_heads;
-  const dim3 grid((max_count * rep + kRows - 1) / kRows, n_entries * a.kv_heads, splits);
+  const dim3 grid(n_entries * a.kv_heads, (max_count * rep + kRows - 1) / kRows, splits);
+  if (grid.y > 65535u) return KLLM_E_UNSUPPORTED;
   attention_mma_kernel<DIM, VDIM><<<grid, kThreads, smem, s>>>(
       a, static_cast<const __nv_bfloat16*>(q), kv, ent_first, ent_count, ent_seq, ent_pos0, splits, ws,
       a.gate ? gates : nullptr, static_cast<__nv_bfloat16*>(out));
