@@ -42,7 +42,7 @@ def one_layer(tmp_path, **kw):
 
 
 @pytest.mark.parametrize("case", ["attention_only", "no_temperature", "no_shared", "experts_only", "top1", "mha",
-                                  "one_kv_head", "scale_const"])
+                                  "one_kv_head", "scale_const", "many_experts", "big_heads"])
 def test_mechanism_alone(tmp_path, case):
     kw = dict(width=48, vocab=50, heads=4, kv_heads=2, dim=12, vdim=20, experts=4, top=2, ff=16, shared_ff=24)
     if case == "attention_only":
@@ -59,6 +59,10 @@ def test_mechanism_alone(tmp_path, case):
         kw.update(kv_heads=1)
     elif case == "scale_const":
         kw.update(scale=0.31)
+    elif case == "many_experts":  # more experts than a warp has lanes
+        kw.update(experts=40, top=5)
+    elif case == "big_heads":     # past the sizes the tensor-core attention is compiled for
+        kw.update(dim=136, vdim=200, heads=2, kv_heads=1)
     cfg, w, d = one_layer(tmp_path, **kw)
     if case == "experts_only":  # the mixer's output projection is zero: what is left of the layer is the feed-forward
         w["l0.mix.o"] = torch.zeros_like(w["l0.mix.o"])
@@ -82,6 +86,26 @@ def test_residual_after_every_layer_run(base):
     assert len(resid_ref) == 1 + 2 * 2  # layer 0, then layers 1..2 twice
     for r, ref in enumerate(resid_ref):
         assert np.abs(got[r] - ref.numpy()).max() < 1e-4 * max(1.0, float(ref.abs().max())), f"layer run {r}"
+
+
+@pytest.mark.parametrize("loop,runs", [((0, 2, 3), 7), ((1, 2, 1), 3), ((0, 3, 2), 6), ((2, 3, 4), 6), (None, 3)])
+def test_loop_shapes(tmp_path, loop, runs):
+    """Three passes, a single pass (its vector is still added once), a loop over every layer, a loop at the end, no loop:
+    every pass has a cache of its own, and the pass vector is added once, right before the pass's first layer."""
+    cfg = make_config(width=40, vocab=60, layers=3, heads=4, kv_heads=2, dim=16, vdim=8, experts=4, top=2, ff=16,
+                      shared_ff=16, loop=loop, q_temp=(0.3, 7))
+    w = make_weights(cfg, seed=101, sharp=2.0)
+    d = write_model(tmp_path, cfg, w)
+    t = toks(45, cfg["vocab"], 102)
+    resid_ref = []
+    ref = forward(cfg, w, t, resid_ref).numpy()
+    assert len(resid_ref) == runs
+    steps = [whole("a", t[:30], end=False)] + [{"entries": [{"id": "a", "tokens": [x], "want": [0]}]} for x in t[30:]]
+    logits, resid = run_trace(d, steps, residual=True)
+    got = resid[0].reshape(runs, 30, cfg["width"])
+    for r in range(runs):
+        assert np.abs(got[r] - resid_ref[r].numpy()[:30]).max() < 2e-4 * max(1.0, float(resid_ref[r].abs().max())), r
+    assert rel_err(np.concatenate(logits), ref) < TOL32
 
 
 # ---- whole prompts, far keys, page and tile borders -----------------------------------------------------------------
