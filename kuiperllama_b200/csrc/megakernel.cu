@@ -806,8 +806,8 @@ __device__ __forceinline__ float attention_inputs(const Params& P, const Phase& 
 }
 
 // ---- attention: SP CTAs per query head, two phases (mha_kernel.cu:47-110 + rope_kernel.cu) ---------
-// The reference gives a head one CTA and so did round 1: 32 of 148 SMs worked while the rest polled,
-// and the time grew with the context.  Every score (one left-to-right FFMA chain per timestep) and
+// The reference gives a head one CTA; with that, 32 of 148 SMs work while the rest poll,
+// and the time grows with the context.  Every score (one left-to-right FFMA chain per timestep) and
 // every output element (one FFMA chain over the timesteps) is independent of the others, so the work
 // splits over SP CTAs per head WITHOUT touching a single chain -- results stay bit-identical:
 //   scores phase  CTA (head, s) rotates q (and the new key row), takes the K tiles j = s, s + SP, ...

@@ -34,6 +34,7 @@ int main(int argc, char** argv) {
   std::string dir, dtype = "bfloat16", out;
   model::SequenceOptions opt;
   opt.max_tokens = 8192;
+  opt.max_seqs = 256;  // a slot costs one page-table row and one spare page per layer run
   bool residual = false;
   for (int i = 1; i < argc; ++i) {
     const std::string a = argv[i];

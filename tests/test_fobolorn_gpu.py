@@ -278,6 +278,38 @@ def test_bfloat16_prompt_attention_on_the_tensor_cores(tmp_path, sizes):
     assert max(err) < 1.5e-2, f"first bad row {int(np.argmax(np.array(err) >= 1.5e-2))}"
 
 
+@pytest.mark.parametrize("dtype,tol,experts,top", [("float32", TOL32, 6, 2), ("bfloat16", TOL16, 3, 3)])
+def test_sizes_that_fit_no_vector(tmp_path, dtype, tol, experts, top):
+    """Width, inner sizes and head sizes that are not multiples of 8 (nor of 4): no 16-byte row, no tensor-core tile.
+    In bf16 every expert is chosen: at these widths a routing flip under bf16 rounding would drown the comparison."""
+    cfg = make_config(width=44, vocab=77, layers=2, heads=3, kv_heads=1, dim=10, vdim=12, experts=experts, top=top, ff=20,
+                      shared_ff=28, loop=(0, 1, 2), q_temp=(0.2, 9))
+    cfg["layers"][1]["mixer"].update(heads=2, kv_heads=2, dim=7, vdim=5)
+    w = make_weights(cfg, seed=111)
+    d = write_model(tmp_path, cfg, w)
+    t = toks(110, cfg["vocab"], 112)
+    ref = ref_logits(cfg, w, t)
+    steps = [whole("a", t[:100], end=False)] + [{"entries": [{"id": "a", "tokens": [x], "want": [0]}]} for x in t[100:]]
+    logits, _ = run_trace(d, steps, dtype=dtype)
+    got = np.concatenate(logits)
+    err = [rel_err(got[i:i + 1], ref[i:i + 1]) for i in range(len(t))]
+    assert rel_err(got, ref) < tol, f"worst rows {np.argsort(err)[-5:]} {np.sort(err)[-5:]}"
+
+
+def test_many_requests_in_one_batch(base):
+    """More requests than any size constant of the engine: 80 prompts of 1..5 tokens in one step, then decoded together."""
+    cfg, w, d = base
+    reqs = [toks(1 + i % 5, cfg["vocab"], 200 + i) + toks(2, cfg["vocab"], 400 + i) for i in range(80)]
+    steps = [{"entries": [{"id": f"r{i}", "tokens": r[:-2], "want": [len(r) - 3]} for i, r in enumerate(reqs)]}]
+    for j in (2, 1):
+        steps.append({"entries": [{"id": f"r{i}", "tokens": [r[-j]], "want": [0]} for i, r in enumerate(reqs)]})
+    logits, _ = run_trace(d, steps, max_tokens=1024)
+    for i, r in enumerate(reqs):
+        ref = ref_logits(cfg, w, r)[-3:]
+        got = np.stack([logits[0][i], logits[1][i], logits[2][i]])
+        assert rel_err(got, ref) < TOL32, i
+
+
 def test_greedy_generation_through_the_scheduler(base):
     import subprocess
     from kuiperllama_b200 import build
