@@ -682,7 +682,7 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int32_t* __
   }
 }
 
-// ---- pairs grouped by expert (one CTA; the lists are short) --------------------------------------------------------
+// ---- pairs grouped by expert (one CTA) --------------------------------------------------------
 __global__ void sort_pairs_kernel(const int32_t* __restrict__ top_idx, int n_pairs, int experts, int block,
                                   int32_t* __restrict__ counts, int32_t* __restrict__ sorted_pair,
                                   int32_t* __restrict__ block_expert, int cap) {
@@ -714,12 +714,19 @@ __global__ void sort_pairs_kernel(const int32_t* __restrict__ top_idx, int n_pai
     block_expert[b] = ex;
   }
   __syncthreads();
-  // stable fill: each expert's pairs in ascending pair order (one thread per expert walks the list)
-  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+  // stable fill: each expert's pairs in ascending pair order.  A warp per expert walks the list 32 pairs at a time;
+  // a pair's place is the count of matching pairs before it (ballot + population count)
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int e = warp; e < experts; e += nw) {
     int o = off[e];
     if (cnt[e] == 0) continue;
-    for (int p = 0; p < n_pairs; ++p)
-      if (top_idx[p] == e) sorted_pair[o++] = p;
+    for (int base = 0; base < n_pairs; base += 32) {
+      const int p = base + lane;
+      const bool mine = p < n_pairs && top_idx[p] == e;
+      const unsigned m = __ballot_sync(kAll, mine);
+      if (mine) sorted_pair[o + __popc(m & ((1u << lane) - 1u))] = p;
+      o += __popc(m);
+    }
   }
 }
 
