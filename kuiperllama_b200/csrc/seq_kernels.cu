@@ -331,7 +331,9 @@ __global__ void qk_prepare_kernel(AttnShape a, const float* __restrict__ qkvg, c
 // SPARSE: the launch has tiles with few rows (decode steps: heads / kv_heads rows) -- rows that do not exist are skipped
 // and the key tiles come in with 16-byte loads; otherwise (prompts) every loop is fully unrolled over the 16 rows of a
 // thread.
-template <typename AT, int C, bool SPARSE>
+// RS: rows a thread keeps in registers -- 16 for full tiles; sparse tiles of at most 8 rows are compiled with 4, so that
+// the unrolled row loops do not issue twelve predicated-off iterations per step.
+template <typename AT, int C, bool SPARSE, int RS>
 __global__ void __launch_bounds__(kAttnThreads)
 attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_t* __restrict__ ent_first,
                  const int32_t* __restrict__ ent_count, const int32_t* __restrict__ ent_seq,
@@ -376,7 +378,8 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
   }
   // this thread's part of the score tile and of the output
   const int key = tid % kAttnKeys, rg = tid / kAttnKeys;  // rows rg*16 .. rg*16+15
-  constexpr int RPT = kAttnRows / (kAttnThreads / kAttnKeys);  // 16
+  constexpr int RPT = RS;
+  static_assert(SPARSE || RS == kAttnRows / (kAttnThreads / kAttnKeys), "a full tile gives each thread group 16 rows");
   float acc[RPT][C];
 #pragma unroll
   for (int i = 0; i < RPT; ++i)
@@ -399,9 +402,9 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
     if (vec_tiles) {  // 16-byte loads: a key's row is dim / V chunks
       constexpr int V = VecOf<AT>::N;
       const int kc = a.dim / V, vc = a.vdim / V;
-      // four chunks per thread are in flight before the first is stored: a split of a decode step has one or two
+      // eight chunks per thread are in flight before the first is stored: a split of a decode step has one or two
       // tiles, so the tile's load latency is paid once, not once per chunk
-      constexpr int U = 4;
+      constexpr int U = 8;
       const int total = kAttnKeys * (kc + vc);
       for (int base = tid; base < total; base += kAttnThreads * U) {
         float f[U][V];
@@ -783,7 +786,7 @@ size_t attention_workspace_bytes(const AttnShape& a, int T, int splits) {
   return static_cast<size_t>(T) * a.heads * splits * (a.vdim + 2) * sizeof(float);
 }
 
-template <typename AT, int C, bool SPARSE>
+template <typename AT, int C, bool SPARSE, int RS>
 static int launch_attention_cs(const AttnShape& a, const void* q, const PagedKV& kv, int n_entries,
                               const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
                               const int32_t* ent_pos0, int max_count, int splits, float* ws, cudaStream_t s) {
@@ -793,14 +796,14 @@ static int launch_attention_cs(const AttnShape& a, const void* q, const PagedKV&
   if (smem > 220 * 1024) return KLLM_E_UNSUPPORTED;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
-    const cudaError_t e = cudaFuncSetAttribute(attention_kernel<AT, C, SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    const cudaError_t e = cudaFuncSetAttribute(attention_kernel<AT, C, SPARSE, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                static_cast<int>(smem));
     if (e != cudaSuccess) return cuda_rc(e);
     configured = smem;
   }
   const int rep = a.heads / a.kv_heads;
   const dim3 grid((max_count * rep + kAttnRows - 1) / kAttnRows, n_entries * a.kv_heads, splits);
-  attention_kernel<AT, C, SPARSE><<<grid, kAttnThreads, smem, s>>>(a, static_cast<const AT*>(q), kv, ent_first, ent_count,
+  attention_kernel<AT, C, SPARSE, RS><<<grid, kAttnThreads, smem, s>>>(a, static_cast<const AT*>(q), kv, ent_first, ent_count,
                                                           ent_seq, ent_pos0, splits, ws);
   return done();
 }
@@ -810,9 +813,12 @@ static int launch_attention_c(const AttnShape& a, const void* q, const PagedKV& 
                               const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
                               const int32_t* ent_pos0, int max_count, int splits, float* ws, cudaStream_t s) {
   if (max_count * (a.heads / a.kv_heads) < kAttnRows)
-    return launch_attention_cs<AT, C, true>(a, q, kv, n_entries, ent_first, ent_count, ent_seq, ent_pos0, max_count, splits,
+    return max_count * (a.heads / a.kv_heads) <= 8
+               ? launch_attention_cs<AT, C, true, 4>(a, q, kv, n_entries, ent_first, ent_count, ent_seq, ent_pos0, max_count,
+                                                     splits, ws, s)
+               : launch_attention_cs<AT, C, true, 16>(a, q, kv, n_entries, ent_first, ent_count, ent_seq, ent_pos0, max_count, splits,
                                             ws, s);
-  return launch_attention_cs<AT, C, false>(a, q, kv, n_entries, ent_first, ent_count, ent_seq, ent_pos0, max_count, splits,
+  return launch_attention_cs<AT, C, false, 16>(a, q, kv, n_entries, ent_first, ent_count, ent_seq, ent_pos0, max_count, splits,
                                            ws, s);
 }
 
