@@ -86,8 +86,8 @@ class FobolornShape:
     top: int
     ff: int
     shared_ff: int
-    temp: tuple = (0.5, 128)
-    eps: float = 1e-6
+    temp: tuple = (0.25, 512)
+    eps: float = 1e-5
 
     @property
     def runs(self):
