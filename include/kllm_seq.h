@@ -26,12 +26,27 @@ extern "C" {
 #define KLLM_SEQ_BF16 1
 
 #define KLLM_SEQ_MIXER_ATTENTION 1 /* softmax attention over the sequence's cached keys */
+#define KLLM_SEQ_MIXER_LATENT 2    /* softmax attention through a low-rank latent: only the latent and one rotated key part are cached */
+#define KLLM_SEQ_MIXER_LINEAR 3    /* linear attention with a decayed matrix state per head (no cache, a recurrent state) */
 #define KLLM_SEQ_FF_NONE 0
-#define KLLM_SEQ_FF_MOE 1 /* softmax router, top-k SwiGLU experts, optional gated shared expert */
+#define KLLM_SEQ_FF_MOE 1   /* routed experts (softmax or sigmoid router), optional gated shared expert */
+#define KLLM_SEQ_FF_DENSE 2 /* down(act(up h)) */
+
+#define KLLM_SEQ_NORM_LAYER 0 /* (v - mean) / sqrt(var + eps) * w + b */
+#define KLLM_SEQ_NORM_RMS 1   /* v / sqrt(mean(v^2) + eps) * w */
+
+/* activations of a feed-forward's inner layer */
+#define KLLM_SEQ_ACT_SWIGLU 0 /* silu(gate h) * (up h): the weights hold gate rows, then up rows */
+#define KLLM_SEQ_ACT_RELU2 1  /* max(up h, 0)^2 */
+#define KLLM_SEQ_ACT_XIELU 2  /* z > 0: a z^2 + z / 2;  z <= 0: b (exp(z) - 1 - z) + z / 2 */
+
+#define KLLM_SEQ_ROUTER_SOFTMAX 0 /* scores = softmax(z); weights = chosen scores / their sum * scale */
+#define KLLM_SEQ_ROUTER_SIGMOID 1 /* scores = sigmoid(z); chosen by score + correction, inside the best groups; weights = score * scale */
 
 typedef struct kllm_seq_norm {
   const float* w; /* [width] */
   const float* b; /* [width] or NULL */
+  int32_t kind;   /* KLLM_SEQ_NORM_* */
 } kllm_seq_norm;
 
 typedef struct kllm_seq_attention {
@@ -47,9 +62,46 @@ typedef struct kllm_seq_attention {
   const void* w_out;     /* [width, heads*vdim], compute type */
 } kllm_seq_attention;
 
+/* Attention through a latent.  Queries: cq = RMSnorm(W_dq h), q = W_uq cq, per head [dim plain | rot_dim rotated].
+ * Keys / values: W_dkv h = [kv_rank | rot_dim]; c = RMSnorm(first part) is the latent, the second part, rotated, is a key
+ * part shared by all heads.  Per head k = [W_uk c | rotated part], v = W_uv c.  Only c and the rotated part are cached:
+ * the engine scores with W_uk^T q against c and applies W_uv after the weighted sum of latents. */
+typedef struct kllm_seq_latent {
+  int32_t heads, dim, rot_dim, vdim, q_rank, kv_rank;
+  float scale;        /* score = (q . k) * scale */
+  int32_t window;     /* position i sees j with 0 <= i - j < window; 0: all earlier positions */
+  int32_t rope_dims;  /* rotary positions on the first rope_dims coordinates of the rotated part, coordinate i paired with i + rope_dims / 2 */
+  float rope_base;    /* angle = position * rope_base^(-2 i / rope_dims) */
+  const void* w_in;   /* [q_rank + kv_rank + rot_dim + heads, width]: W_dq | W_dkv | gate rows, compute type */
+  const float* q_norm_w;  /* [q_rank] */
+  const float* kv_norm_w; /* [kv_rank] */
+  const void* w_uq;   /* [heads * (dim + rot_dim), q_rank] */
+  const void* w_uk;   /* [heads * dim, kv_rank] */
+  const void* w_uv;   /* [heads * vdim, kv_rank] */
+  const float* sink;  /* [heads]: exp(sink) joins the softmax denominator (no key, no value), or NULL */
+  const void* w_out;  /* [width, heads * vdim] */
+} kllm_seq_latent;
+
+/* Linear attention: q, k, v = silu(W h); per head S <- decay * S + k v^T, o = S^T q; the heads together are RMS-normed,
+ * multiplied by sigmoid(W_g h) and projected.  S [dim, vdim] per head is fp32 state of the sequence. */
+typedef struct kllm_seq_linear {
+  int32_t heads, dim, vdim;
+  const float* decay;      /* [heads], device */
+  const void* w_in;        /* [2 * heads * dim + 2 * heads * vdim, width]: q | k | v | gate rows */
+  const float* out_norm_w; /* [heads * vdim] */
+  const void* w_out;       /* [width, heads * vdim] */
+} kllm_seq_linear;
+
+typedef struct kllm_seq_dense {
+  int32_t ff, act;    /* inner size; KLLM_SEQ_ACT_* (XIELU or RELU2) */
+  float act_a, act_b; /* the two coefficients of KLLM_SEQ_ACT_XIELU */
+  const void* up;     /* [ff, width] */
+  const void* down;   /* [width, ff] */
+} kllm_seq_dense;
+
 typedef struct kllm_seq_moe {
   int32_t experts, top, ff; /* routed experts, chosen per token, inner size of a routed expert */
-  float router_scale;       /* weights = chosen softmax scores / (their sum + 1e-20) * router_scale */
+  float router_scale;       /* see KLLM_SEQ_ROUTER_* */
   const float* w_router;    /* [experts, width] fp32 */
   const void* gate_up;      /* [experts][2*ff][width]: gate rows, then up rows; compute type */
   const void* down;         /* [experts][width][ff] */
@@ -57,6 +109,11 @@ typedef struct kllm_seq_moe {
   const void* shared_gate_up; /* [2*shared_ff][width] */
   const void* shared_down;    /* [width][shared_ff] */
   const float* w_shared_gate; /* [width] fp32: the shared expert's output is scaled by sigmoid(w . h); NULL: by 1 */
+  int32_t router_kind;        /* KLLM_SEQ_ROUTER_* */
+  const float* correction;    /* [experts] added to the scores for the choice only (sigmoid router), or NULL */
+  int32_t groups, groups_keep; /* sigmoid router: experts form `groups` equal groups of neighbours, a group scores the sum
+                                  of its two largest choice scores, and only the best groups_keep groups can be chosen; 0: no groups */
+  int32_t act;                /* KLLM_SEQ_ACT_SWIGLU, or KLLM_SEQ_ACT_RELU2 (then gate_up holds [experts][ff][width]) */
 } kllm_seq_moe;
 
 typedef struct kllm_seq_layer {
@@ -66,6 +123,13 @@ typedef struct kllm_seq_layer {
   kllm_seq_norm pre_mixer, post_mixer, pre_ff, post_ff;
   kllm_seq_attention attn;
   kllm_seq_moe moe;
+  /* A norm without weights (w == NULL) after a sublayer means none: x += sublayer(...). */
+  /* token shift: the mixer reads h + (h_prev - h) * shift instead of h = pre_mixer(x), h_prev the previous token's h
+   * (zeros before the first token; the last h of a sequence is part of its state).  [width] fp32 or NULL */
+  const float* shift;
+  kllm_seq_latent latent;
+  kllm_seq_linear linear;
+  kllm_seq_dense dense;
 } kllm_seq_layer;
 
 typedef struct kllm_seq_desc {
@@ -87,6 +151,10 @@ typedef struct kllm_seq_desc {
   int32_t max_tokens; /* tokens all live sequences may hold together */
   int32_t max_seqs;   /* live sequences */
   int32_t page_tokens; /* tokens per page; 0: the engine's default */
+  kllm_seq_norm embed_norm;  /* applied to the embedding rows (w == NULL: none) */
+  const int32_t* run_embed;  /* [n_runs] or NULL: != 0 adds the embedding output (after embed_norm) to the residual stream
+                                before the run, ahead of run_add's vector */
+  float logit_scale;         /* logits = head(...) * logit_scale; 0 means 1 */
 } kllm_seq_desc;
 
 typedef struct kllm_seq_engine kllm_seq_engine;
@@ -113,10 +181,10 @@ int kllm_seq_step(kllm_seq_engine* eng, int32_t n_entries, const int32_t* seqs, 
 int kllm_seq_trace_residual(kllm_seq_engine* eng, float* residual_host);
 /* Measurement aid: the next step records an event after each of its phases and writes the device time spent in every
  * phase class, in milliseconds, to phase_ms[KLLM_SEQ_PHASES] (summed over the layer runs). */
-#define KLLM_SEQ_PHASE_NORM 0       /* embedding rows, residual + layer-norm kernels */
-#define KLLM_SEQ_PHASE_IN_PROJ 1    /* q | k | v | gate product */
-#define KLLM_SEQ_PHASE_QK_PREPARE 2 /* head norms, temperature, cache scatter, gates */
-#define KLLM_SEQ_PHASE_ATTENTION 3  /* paged attention + merge of the key splits */
+#define KLLM_SEQ_PHASE_NORM 0       /* embedding rows, residual + norm kernels, token shift */
+#define KLLM_SEQ_PHASE_IN_PROJ 1    /* q | k | v | gate product (latent: the down-projections) */
+#define KLLM_SEQ_PHASE_QK_PREPARE 2 /* head norms, temperature, rotation, cache scatter, gates; latent: + query up-projection and key absorption */
+#define KLLM_SEQ_PHASE_ATTENTION 3  /* paged attention + merge of the key splits; linear attention; latent: + value expansion */
 #define KLLM_SEQ_PHASE_OUT_PROJ 4
 #define KLLM_SEQ_PHASE_ROUTER 5     /* residual + norms around the router and the router itself (one kernel) */
 #define KLLM_SEQ_PHASE_EXPERTS 6    /* routed experts */

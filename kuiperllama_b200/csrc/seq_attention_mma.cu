@@ -325,6 +325,8 @@ int launch_mma(const AttnShape& a, const void* q, const float* gates, const Page
 
 bool attention_mma_usable(int dtype, const AttnShape& a, int max_count) {
   if (dtype != KLLM_SEQ_BF16 || a.kv_heads <= 0 || a.heads % a.kv_heads) return false;
+  // windows, sinks and fp32 queries / outputs are the split-key kernel's
+  if (a.window > 0 || a.sink != nullptr || a.q_f32 || a.out_f32) return false;
   const bool dims = a.dim % 8 == 0 && a.dim <= 128 && a.vdim % 8 == 0 && a.vdim <= 128;
   // steps of single tokens keep the split-key kernel (and stay capturable: no attribute call on their path)
   return dims && max_count >= 2 && max_count * (a.heads / a.kv_heads) >= 16;

@@ -51,7 +51,7 @@ constexpr int kGroupedMinTokens = 64;  // steps with at least this many tokens r
 constexpr int kGroupBlock = 64;
 constexpr int kSharedRideTokens = 4;   // steps of at most this many tokens run the shared expert inside the pair kernels
 
-inline NormW nw(const kllm_seq_norm& n) { return NormW{n.w, n.b}; }
+inline NormW nw(const kllm_seq_norm& n) { return NormW{n.w, n.b, n.kind}; }
 inline size_t elt(int dtype) { return dtype == KLLM_SEQ_BF16 ? 2 : 4; }
 
 uint64_t g_buffer_generation = 0;  // bumped whenever a workspace moves: captured graphs hold the old addresses
@@ -84,7 +84,11 @@ struct kllm_seq_engine {
   cudaStream_t stream = nullptr;
   // cache
   int page = 0, n_pages = 0, table_stride = 0;
-  std::vector<void*> k_pool, v_pool;  // per run
+  std::vector<void*> k_pool, v_pool;  // per run (null for runs without a cache; a latent run has keys only)
+  // recurrent state per run and slot: the last mixer input of layers with a token shift [max_seqs][width], and the
+  // matrix state of linear attention [max_seqs][heads][dim][vdim]; fp32.  A sequence's state is taken as zero while its
+  // length is 0, so a slot that is used again needs no clearing.
+  std::vector<float*> shift_state, linear_state;
   int32_t* table_dev = nullptr;       // [max_seqs][table_stride]
   std::vector<int32_t> table_host;
   std::vector<int32_t> free_pages;    // kept sorted descending: back() is the lowest number
@@ -98,6 +102,7 @@ struct kllm_seq_engine {
   int32_t* pinned = nullptr;
   size_t pinned_cap = 0;
   DevBuf idx, x, h, proj, q, gates, att, y, y2, ws, top_idx, top_w, sgate, inter, pairs_out, sort, sorted_a, sorted_inter, hw, logits, amax;
+  DevBuf x0, hn, qf, qa, ol;  // embedding output; fp32 normed rows ahead of a token shift; latent / linear attention scratch
   float* logits_pinned = nullptr;
   size_t logits_pinned_cap = 0;
   float* trace_host = nullptr;
@@ -129,10 +134,15 @@ struct kllm_seq_engine {
   }
   // limits over the layers
   int max_proj = 0, max_q = 0, max_att = 0, max_heads = 0, max_top = 0, max_ff = 0, max_sff = 0;
+  int max_qf = 0, max_qa = 0, max_ol = 0;
+  bool any_shift = false, any_run_embed = false;
+  std::vector<int32_t> run_embed;
 
   ~kllm_seq_engine() {
     for (void* p : k_pool) if (p) cudaFree(p);
     for (void* p : v_pool) if (p) cudaFree(p);
+    for (float* p : shift_state) if (p) cudaFree(p);
+    for (float* p : linear_state) if (p) cudaFree(p);
     if (table_dev) cudaFree(table_dev);
     if (pinned) cudaFreeHost(pinned);
     if (logits_pinned) cudaFreeHost(logits_pinned);
@@ -153,19 +163,42 @@ static int validate(const kllm_seq_desc* d) {
   }
   for (int i = 0; i < d->n_layers; ++i) {
     const kllm_seq_layer& L = d->layers[i];
-    if (L.mixer_kind != KLLM_SEQ_MIXER_ATTENTION) return KLLM_E_UNSUPPORTED;
-    const kllm_seq_attention& a = L.attn;
-    if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0 || !a.w_in || !a.w_out ||
-        !L.pre_mixer.w)
-      return KLLM_E_INVALID;
-    if (a.qk_norm && (!a.q_norm_w || !a.k_norm_w)) return KLLM_E_INVALID;
-    if (a.vdim > 256 || a.dim > 512) return KLLM_E_UNSUPPORTED;
+    if (!L.pre_mixer.w) return KLLM_E_INVALID;
+    if (L.mixer_kind == KLLM_SEQ_MIXER_ATTENTION) {
+      const kllm_seq_attention& a = L.attn;
+      if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0 || !a.w_in || !a.w_out)
+        return KLLM_E_INVALID;
+      if (a.qk_norm && (!a.q_norm_w || !a.k_norm_w)) return KLLM_E_INVALID;
+      if (a.vdim > 256 || a.dim > 512) return KLLM_E_UNSUPPORTED;
+    } else if (L.mixer_kind == KLLM_SEQ_MIXER_LATENT) {
+      const kllm_seq_latent& a = L.latent;
+      if (a.heads <= 0 || a.dim <= 0 || a.rot_dim < 0 || a.vdim <= 0 || a.q_rank <= 0 || a.kv_rank <= 0 || a.window < 0 ||
+          a.rope_dims < 0 || a.rope_dims > a.rot_dim || (a.rope_dims & 1) || (a.rope_dims > 0 && a.rope_base <= 0.f) ||
+          !a.w_in || !a.q_norm_w || !a.kv_norm_w || !a.w_uq || !a.w_uk || !a.w_uv || !a.w_out)
+        return KLLM_E_INVALID;
+      // the latent is the value of the paged attention kernel, latent + rotated part its key
+      if (a.kv_rank > 256 || a.kv_rank + a.rot_dim > 512) return KLLM_E_UNSUPPORTED;
+    } else if (L.mixer_kind == KLLM_SEQ_MIXER_LINEAR) {
+      const kllm_seq_linear& a = L.linear;
+      if (a.heads <= 0 || a.dim <= 0 || a.vdim <= 0 || !a.decay || !a.w_in || !a.out_norm_w || !a.w_out) return KLLM_E_INVALID;
+      if (a.dim > 256) return KLLM_E_UNSUPPORTED;
+    } else {
+      return KLLM_E_UNSUPPORTED;
+    }
     if (L.ff_kind == KLLM_SEQ_FF_MOE) {
       const kllm_seq_moe& m = L.moe;
       if (m.experts <= 0 || m.top <= 0 || m.top > m.experts || m.ff <= 0 || !m.w_router || !m.gate_up || !m.down ||
           !L.pre_ff.w)
         return KLLM_E_INVALID;
       if (m.shared_ff > 0 && (!m.shared_gate_up || !m.shared_down)) return KLLM_E_INVALID;
+      if (m.act != KLLM_SEQ_ACT_SWIGLU && (m.act != KLLM_SEQ_ACT_RELU2 || m.shared_ff > 0)) return KLLM_E_UNSUPPORTED;
+      if (m.router_kind != KLLM_SEQ_ROUTER_SOFTMAX && m.router_kind != KLLM_SEQ_ROUTER_SIGMOID) return KLLM_E_UNSUPPORTED;
+      if (m.groups < 0 || (m.groups > 0 && (m.experts % m.groups != 0 || m.groups_keep <= 0 || m.groups_keep > m.groups)))
+        return KLLM_E_INVALID;
+    } else if (L.ff_kind == KLLM_SEQ_FF_DENSE) {
+      const kllm_seq_dense& f = L.dense;
+      if (f.ff <= 0 || !f.up || !f.down || !L.pre_ff.w) return KLLM_E_INVALID;
+      if (f.act != KLLM_SEQ_ACT_XIELU && f.act != KLLM_SEQ_ACT_RELU2) return KLLM_E_UNSUPPORTED;
     } else if (L.ff_kind != KLLM_SEQ_FF_NONE) {
       return KLLM_E_UNSUPPORTED;
     }
@@ -189,6 +222,10 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
   e->d.layers = e->layers.data();
   e->d.run_layer = e->run_layer.data();
   e->d.run_add = e->run_add.data();
+  e->run_embed.assign(desc->n_runs, 0);
+  if (desc->run_embed) e->run_embed.assign(desc->run_embed, desc->run_embed + desc->n_runs);
+  e->d.run_embed = e->run_embed.data();
+  for (int32_t v : e->run_embed) e->any_run_embed = e->any_run_embed || v != 0;
   e->stream = static_cast<cudaStream_t>(stream);
   if (e->stream == nullptr) {  // a stream of its own: the legacy default stream cannot be captured
     if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) {
@@ -207,16 +244,30 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
   for (int p = e->n_pages - 1; p >= 0; --p) e->free_pages.push_back(p);
   const size_t es = elt(desc->dtype);
   for (int r = 0; r < desc->n_runs; ++r) {
-    const kllm_seq_attention& a = e->layers[e->run_layer[r]].attn;
+    const kllm_seq_layer& L = e->layers[e->run_layer[r]];
     void *k = nullptr, *v = nullptr;
-    const size_t rows = static_cast<size_t>(e->n_pages) * e->page * a.kv_heads;
-    if (cudaMalloc(&k, rows * a.dim * es) != cudaSuccess || cudaMalloc(&v, rows * a.vdim * es) != cudaSuccess) {
-      if (k) cudaFree(k);
+    float *sh = nullptr, *ls = nullptr;
+    const size_t tokens = static_cast<size_t>(e->n_pages) * e->page;
+    bool ok = true;
+    if (L.mixer_kind == KLLM_SEQ_MIXER_ATTENTION) {
+      const kllm_seq_attention& a = L.attn;
+      ok = cudaMalloc(&k, tokens * a.kv_heads * a.dim * es) == cudaSuccess &&
+           cudaMalloc(&v, tokens * a.kv_heads * a.vdim * es) == cudaSuccess;
+    } else if (L.mixer_kind == KLLM_SEQ_MIXER_LATENT) {
+      ok = cudaMalloc(&k, tokens * (L.latent.kv_rank + L.latent.rot_dim) * es) == cudaSuccess;
+    } else {
+      const size_t n = static_cast<size_t>(desc->max_seqs) * L.linear.heads * L.linear.dim * L.linear.vdim;
+      ok = cudaMalloc(&ls, n * sizeof(float)) == cudaSuccess;
+    }
+    if (ok && L.shift) ok = cudaMalloc(&sh, static_cast<size_t>(desc->max_seqs) * desc->width * sizeof(float)) == cudaSuccess;
+    e->k_pool.push_back(k);
+    e->v_pool.push_back(v);
+    e->shift_state.push_back(sh);
+    e->linear_state.push_back(ls);
+    if (!ok) {
       delete e;
       return static_cast<int>(cudaErrorMemoryAllocation);
     }
-    e->k_pool.push_back(k);
-    e->v_pool.push_back(v);
   }
   if (cudaMalloc(&e->table_dev, e->table_host.size() * sizeof(int32_t)) != cudaSuccess) {
     delete e;
@@ -224,11 +275,32 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
   }
   cudaMemset(e->table_dev, 0, e->table_host.size() * sizeof(int32_t));
   for (const kllm_seq_layer& L : e->layers) {
-    const kllm_seq_attention& a = L.attn;
-    e->max_proj = std::max(e->max_proj, a.heads * a.dim + a.kv_heads * (a.dim + a.vdim) + (a.gate ? a.heads : 0));
-    e->max_q = std::max(e->max_q, a.heads * a.dim);
-    e->max_att = std::max(e->max_att, a.heads * a.vdim);
-    e->max_heads = std::max(e->max_heads, a.heads);
+    e->any_shift = e->any_shift || L.shift != nullptr;
+    if (L.mixer_kind == KLLM_SEQ_MIXER_ATTENTION) {
+      const kllm_seq_attention& a = L.attn;
+      e->max_proj = std::max(e->max_proj, a.heads * a.dim + a.kv_heads * (a.dim + a.vdim) + (a.gate ? a.heads : 0));
+      e->max_q = std::max(e->max_q, a.heads * a.dim);
+      e->max_att = std::max(e->max_att, a.heads * a.vdim);
+      e->max_heads = std::max(e->max_heads, a.heads);
+    } else if (L.mixer_kind == KLLM_SEQ_MIXER_LATENT) {
+      const kllm_seq_latent& a = L.latent;
+      e->max_proj = std::max(e->max_proj, a.q_rank + a.kv_rank + a.rot_dim + a.heads);
+      e->max_q = std::max(e->max_q, a.q_rank);
+      e->max_qf = std::max(e->max_qf, a.heads * (a.dim + a.rot_dim));
+      e->max_qa = std::max(e->max_qa, a.heads * (a.kv_rank + a.rot_dim));
+      e->max_ol = std::max(e->max_ol, a.heads * a.kv_rank);
+      e->max_att = std::max(e->max_att, a.heads * a.vdim);
+      e->max_heads = std::max(e->max_heads, a.heads);
+    } else {
+      const kllm_seq_linear& a = L.linear;
+      e->max_proj = std::max(e->max_proj, 2 * a.heads * (a.dim + a.vdim));
+      e->max_ol = std::max(e->max_ol, a.heads * a.vdim);
+      e->max_att = std::max(e->max_att, a.heads * a.vdim);
+    }
+    if (L.ff_kind == KLLM_SEQ_FF_DENSE) {
+      e->max_proj = std::max(e->max_proj, L.dense.ff);
+      e->max_att = std::max(e->max_att, L.dense.ff);
+    }
     if (L.ff_kind == KLLM_SEQ_FF_MOE) {
       e->max_top = std::max(e->max_top, L.moe.top);
       e->max_ff = std::max(e->max_ff, L.moe.top * L.moe.ff);
@@ -382,18 +454,34 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       while (splits < want) splits *= 2;  // a power of two: few distinct launch shapes as a context grows
     }
   }
+  // a layer with a window never has more key tiles in reach than the window spans: a function of `splits` and the
+  // layer's constants only, so that captured decode steps stay keyed by `splits`
+  auto window_splits = [&](int window) {
+    if (window <= 0) return splits;
+    int cap = 1;
+    while (cap < window / kAttnKeys + 2) cap *= 2;
+    return std::min(splits, cap);
+  };
   const size_t Ts = static_cast<size_t>(T);
   RC(e->x.reserve(Ts * W * 4));
   RC(e->h.reserve(Ts * W * es));
   RC(e->proj.reserve(Ts * std::max({e->max_proj, 2 * e->max_sff, W}) * 4));
-  RC(e->q.reserve(Ts * e->max_q * es));
-  RC(e->gates.reserve(Ts * e->max_heads * 4));
+  RC(e->q.reserve(Ts * std::max(1, e->max_q) * es));
+  RC(e->gates.reserve(Ts * std::max(1, e->max_heads) * 4));
   RC(e->att.reserve(Ts * std::max(e->max_att, e->max_sff) * es));
   RC(e->y.reserve(Ts * W * 4));
   RC(e->y2.reserve(Ts * W * 4));
+  if (e->any_run_embed) RC(e->x0.reserve(Ts * W * 4));
+  if (e->any_shift) RC(e->hn.reserve(Ts * W * 4));
+  if (e->max_qf > 0) RC(e->qf.reserve(Ts * e->max_qf * 4));
+  if (e->max_qa > 0) RC(e->qa.reserve(Ts * e->max_qa * 4));
+  if (e->max_ol > 0) RC(e->ol.reserve(Ts * e->max_ol * 4));
   size_t ws_bytes = 0;
   for (const kllm_seq_layer& L : e->layers) {
-    AttnShape a{L.attn.heads, L.attn.kv_heads, L.attn.dim, L.attn.vdim, 0, 0, 0, 0, 0};
+    AttnShape a{};
+    if (L.mixer_kind == KLLM_SEQ_MIXER_ATTENTION) a.heads = L.attn.heads, a.vdim = L.attn.vdim;
+    else if (L.mixer_kind == KLLM_SEQ_MIXER_LATENT) a.heads = L.latent.heads, a.vdim = L.latent.kv_rank;
+    else continue;
     ws_bytes = std::max(ws_bytes, attention_workspace_bytes(a, T, splits));
   }
   RC(e->ws.reserve(ws_bytes));
@@ -415,55 +503,124 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   float* y = static_cast<float*>(e->y.p);
   float* y2 = static_cast<float*>(e->y2.p);
   const bool tracing = e->trace_host != nullptr;
+  bool single = true;  // every entry brings one token: a row's CTA owns its sequence's state
+  for (int i = 0; i < n_entries; ++i) single = single && counts[i] == 1;
 
   // ---- device: the layer runs -------------------------------------------------------------------------------------
   e->prof_used = 0;
   e->prof_phase.clear();
   e->mark(-1);
   auto run_device = [&]() -> int {
-  RC(launch_embed(dtype, d.embed, d_tok, x, T, W, st));
+  RC(launch_embed(dtype, d.embed, d_tok, x, e->any_run_embed ? static_cast<float*>(e->x0.p) : nullptr, nw(d.embed_norm),
+                  d.norm_eps, T, W, st));
   e->mark(KLLM_SEQ_PHASE_NORM);
-  bool pre_done = false;  // the previous run's last kernel already produced this run's h (and added its vector)
+  // What comes ahead of run r's mixer rides on one norm kernel (`a` may already carry the end of the run before):
+  // the embedding output and the run's vector are added, the pre-norm is taken, and the token shift is applied -- inside
+  // the kernel when every entry is one token, else by a kernel of its own on the fp32 rows.
+  auto launch_pre = [&](ResidNormArgs a, int r, int phase) -> int {
+    const kllm_seq_layer& L = e->layers[e->run_layer[r]];
+    a.x = x, a.T = T, a.width = W, a.dtype = dtype, a.eps = d.norm_eps;
+    a.add = e->run_add[r] >= 0 ? d.run_vectors + static_cast<size_t>(e->run_add[r]) * W : nullptr;
+    a.add_rows = e->run_embed[r] ? static_cast<const float*>(e->x0.p) : nullptr;
+    a.pre = nw(L.pre_mixer), a.out = e->h.p;
+    const bool shift_after = L.shift != nullptr && !single;
+    if (L.shift != nullptr && single) a.shift = ShiftArgs{L.shift, e->shift_state[r], d_seq, d_pos};
+    if (shift_after) a.out_f32 = static_cast<float*>(e->hn.p);
+    RC(launch_resid_norm(a, st));
+    if (shift_after)
+      RC(launch_token_shift(dtype, static_cast<const float*>(e->hn.p), L.shift, e->shift_state[r], d_seq, d_pos, d_first,
+                            d_count, n_entries, e->h.p, T, W, st));
+    e->mark(phase);
+    return 0;
+  };
+  bool pre_done = false;  // the previous run's last kernel already produced this run's h
   for (int r = 0; r < d.n_runs; ++r) {
     const kllm_seq_layer& L = e->layers[e->run_layer[r]];
-    const kllm_seq_attention& A = L.attn;
-    const AttnShape shape{A.heads, A.kv_heads, A.dim, A.vdim, A.scale, A.temp_coef, A.temp_every, A.qk_norm, A.gate};
-    const PagedKV kv{e->k_pool[r], e->v_pool[r], e->table_dev, e->table_stride, e->page};
-    if (!pre_done) {
-      ResidNormArgs a{};
-      a.x = x, a.add = e->run_add[r] >= 0 ? d.run_vectors + static_cast<size_t>(e->run_add[r]) * W : nullptr;
-      a.pre = nw(L.pre_mixer), a.out = e->h.p, a.T = T, a.width = W, a.dtype = dtype, a.eps = d.norm_eps;
+    if (!pre_done) RC(launch_pre(ResidNormArgs{}, r, KLLM_SEQ_PHASE_NORM));
+    pre_done = false;
+    if (L.mixer_kind == KLLM_SEQ_MIXER_ATTENTION) {
+      const kllm_seq_attention& A = L.attn;
+      const AttnShape shape{A.heads, A.kv_heads, A.dim, A.vdim, A.scale, A.temp_coef, A.temp_every, A.qk_norm, A.gate,
+                            0, nullptr, 0, 0};
+      const PagedKV kv{e->k_pool[r], e->v_pool[r], e->table_dev, e->table_stride, e->page, A.kv_heads * A.dim,
+                       A.kv_heads * A.vdim};
+      const int n_proj = A.heads * A.dim + A.kv_heads * (A.dim + A.vdim) + (A.gate ? A.heads : 0);
+      RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, n_proj, st));
+      e->mark(KLLM_SEQ_PHASE_IN_PROJ);
+      RC(launch_qk_prepare(dtype, shape, proj, A.q_norm_w, A.k_norm_w, d.norm_eps, d_seq, d_pos, e->q.p,
+                           static_cast<float*>(e->gates.p), kv, T, st));
+      e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
+      RC(launch_attention(dtype, shape, e->q.p, static_cast<const float*>(e->gates.p), kv, n_entries, d_first, d_count,
+                          d_eseq, d_pos0, max_count, max_ctx, splits, static_cast<float*>(e->ws.p), e->att.p, T, d_seq,
+                          d_pos, st));
+      e->mark(KLLM_SEQ_PHASE_ATTENTION);
+      RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
+      e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
+    } else if (L.mixer_kind == KLLM_SEQ_MIXER_LATENT) {
+      const kllm_seq_latent& A = L.latent;
+      const LatentShape ls{A.heads, A.dim, A.rot_dim, A.vdim, A.q_rank, A.kv_rank, A.rope_dims, A.rope_base};
+      const int krow = A.kv_rank + A.rot_dim;
+      const PagedKV kv{e->k_pool[r], e->k_pool[r], e->table_dev, e->table_stride, e->page, krow, krow};
+      float* gates = static_cast<float*>(e->gates.p);
+      RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, A.q_rank + krow + A.heads, st));
+      e->mark(KLLM_SEQ_PHASE_IN_PROJ);
+      RC(launch_latent_prepare(dtype, ls, proj, A.q_norm_w, A.kv_norm_w, d.norm_eps, d_seq, d_pos, e->q.p, gates, kv, T, st));
+      RC(gemm(dtype, e->q.p, A.w_uq, static_cast<float*>(e->qf.p), T, A.q_rank, A.heads * (A.dim + A.rot_dim), st));
+      RC(launch_latent_absorb(dtype, ls, static_cast<const float*>(e->qf.p), A.w_uk, d_pos, static_cast<float*>(e->qa.p), T, st));
+      e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
+      // one shared key/value "head": keys [latent | rotated part], values the latent itself
+      const AttnShape shape{A.heads, 1, krow, A.kv_rank, A.scale, 0.f, 0, 0, 1, A.window, A.sink, 1, 1};
+      RC(launch_attention(dtype, shape, e->qa.p, gates, kv, n_entries, d_first, d_count, d_eseq, d_pos0, max_count, max_ctx,
+                          window_splits(A.window), static_cast<float*>(e->ws.p), e->ol.p, T, d_seq, d_pos, st));
+      RC(launch_latent_expand(dtype, ls, static_cast<const float*>(e->ol.p), A.w_uv, e->att.p, T, st));
+      e->mark(KLLM_SEQ_PHASE_ATTENTION);
+      RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
+      e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
+    } else {
+      const kllm_seq_linear& A = L.linear;
+      RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, 2 * A.heads * (A.dim + A.vdim), st));
+      e->mark(KLLM_SEQ_PHASE_IN_PROJ);
+      RC(launch_linear_attention(A.heads, A.dim, A.vdim, A.decay, proj, e->linear_state[r], n_entries, d_first, d_count,
+                                 d_eseq, d_pos0, max_count, static_cast<float*>(e->ol.p), st));
+      RC(launch_linear_out(dtype, A.heads, A.dim, A.vdim, static_cast<const float*>(e->ol.p), proj, A.out_norm_w, d.norm_eps,
+                           e->att.p, T, st));
+      e->mark(KLLM_SEQ_PHASE_ATTENTION);
+      RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
+      e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
+    }
+
+    // what follows this layer run: the next run's additions and pre-norm can ride on this run's last kernel
+    const bool fuse_next = r + 1 < d.n_runs && !tracing;
+    auto end_of_run = [&](ResidNormArgs a) -> int {  // `a` holds what the run still adds to x
+      if (fuse_next) {
+        pre_done = true;
+        return launch_pre(a, r + 1, KLLM_SEQ_PHASE_NORM);
+      }
+      a.x = x, a.T = T, a.width = W, a.dtype = dtype, a.eps = d.norm_eps;
       RC(launch_resid_norm(a, st));
       e->mark(KLLM_SEQ_PHASE_NORM);
-    }
-    pre_done = false;
-    const int n_proj = A.heads * A.dim + A.kv_heads * (A.dim + A.vdim) + (A.gate ? A.heads : 0);
-    RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, n_proj, st));
-    e->mark(KLLM_SEQ_PHASE_IN_PROJ);
-    RC(launch_qk_prepare(dtype, shape, proj, A.q_norm_w, A.k_norm_w, d.norm_eps, d_seq, d_pos, e->q.p,
-                         static_cast<float*>(e->gates.p), kv, T, st));
-    e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
-    RC(launch_attention(dtype, shape, e->q.p, static_cast<const float*>(e->gates.p), kv, n_entries, d_first, d_count,
-                        d_eseq, d_pos0, max_count, max_ctx, splits, static_cast<float*>(e->ws.p), e->att.p, T, d_seq,
-                        d_pos, st));
-    e->mark(KLLM_SEQ_PHASE_ATTENTION);
-    RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
-    e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
-
-    // what follows this layer run: the next run's vector and pre-norm can ride on this run's last kernel
-    const bool last = r + 1 == d.n_runs;
-    const float* next_add = nullptr;
-    NormW next_pre{nullptr, nullptr};
-    if (!last && !tracing) {
-      next_add = e->run_add[r + 1] >= 0 ? d.run_vectors + static_cast<size_t>(e->run_add[r + 1]) * W : nullptr;
-      next_pre = nw(e->layers[e->run_layer[r + 1]].pre_mixer);
-    }
+      return 0;
+    };
     if (L.ff_kind == KLLM_SEQ_FF_NONE) {
       ResidNormArgs a{};
-      a.x = x, a.y1 = y, a.post = nw(L.post_mixer), a.T = T, a.width = W, a.dtype = dtype, a.eps = d.norm_eps;
-      if (next_pre.w) a.add = next_add, a.pre = next_pre, a.out = e->h.p, pre_done = true;
-      RC(launch_resid_norm(a, st));
-      e->mark(KLLM_SEQ_PHASE_NORM);
+      a.y1 = y, a.post = nw(L.post_mixer);
+      RC(end_of_run(a));
+    } else if (L.ff_kind == KLLM_SEQ_FF_DENSE) {
+      const kllm_seq_dense& F = L.dense;
+      {
+        ResidNormArgs a{};
+        a.x = x, a.y1 = y, a.post = nw(L.post_mixer), a.pre = nw(L.pre_ff), a.out = e->h.p, a.T = T, a.width = W;
+        a.dtype = dtype, a.eps = d.norm_eps;
+        RC(launch_resid_norm(a, st));
+        e->mark(KLLM_SEQ_PHASE_ROUTER);
+      }
+      RC(gemm(dtype, e->h.p, F.up, proj, T, W, F.ff, st));
+      RC(launch_activation(dtype, F.act, F.act_a, F.act_b, proj, e->att.p, Ts * F.ff, st));
+      RC(gemm(dtype, e->att.p, F.down, y, T, F.ff, W, st));
+      e->mark(KLLM_SEQ_PHASE_EXPERTS);
+      ResidNormArgs a{};
+      a.y1 = y, a.post = nw(L.post_ff);
+      RC(end_of_run(a));
     } else {
       const kllm_seq_moe& M = L.moe;
       int32_t* top_idx = static_cast<int32_t*>(e->top_idx.p);
@@ -474,7 +631,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
         a.x = x, a.y1 = y, a.post = nw(L.post_mixer), a.pre = nw(L.pre_ff), a.out = e->h.p, a.T = T, a.width = W;
         a.dtype = dtype, a.eps = d.norm_eps;
         a.router = RouterArgs{M.w_router, M.shared_ff > 0 ? M.w_shared_gate : nullptr, M.experts, M.top, M.router_scale,
-                              top_idx, top_w, sgate};
+                              top_idx, top_w, sgate, M.router_kind, M.correction, M.groups, M.groups_keep};
         RC(launch_resid_norm(a, st));
         e->mark(KLLM_SEQ_PHASE_ROUTER);
       }
@@ -486,7 +643,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
           sh = SharedExpert{M.shared_gate_up, M.shared_down, M.w_shared_gate ? sgate : nullptr, e->att.p, M.shared_ff};
           shared_done = true;
         }
-        RC(launch_expert_gate_up(dtype, e->h.p, M.gate_up, top_idx, e->inter.p, T, M.top, M.ff, W, sh, st));
+        RC(launch_expert_gate_up(dtype, e->h.p, M.gate_up, top_idx, e->inter.p, T, M.top, M.ff, W, sh, M.act, st));
         RC(launch_expert_down(dtype, e->inter.p, M.down, top_idx, top_w, y, T, M.top, M.ff, W, sh, st));
       } else {
         const int n_pairs = T * M.top;
@@ -500,18 +657,19 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
         GroupedArgs g{};
         g.sorted_pair = sorted, g.block_expert = block_expert, g.n_blocks = n_blocks, g.block = kGroupBlock;
         g.experts = M.experts;
+        const int inner_epilogue = M.act == KLLM_SEQ_ACT_RELU2 ? 2 : 1;
         if (grouped_tensor_core_usable(dtype, W, M.ff)) {
           // rows in sorted order: a gathered copy of h, the expert's inner activations, then scattered back by pair
           RC(e->sorted_a.reserve(static_cast<size_t>(cap) * W * es));
           RC(e->sorted_inter.reserve(static_cast<size_t>(cap) * M.ff * es));
           RC(gather_rows_bf16(e->h.p, sorted, M.top, e->sorted_a.p, cap, W, st));
           g.sorted_layout = 1;
-          g.a = e->sorted_a.p, g.w = M.gate_up, g.K = W, g.N = M.ff, g.epilogue = 1, g.out = e->sorted_inter.p;
+          g.a = e->sorted_a.p, g.w = M.gate_up, g.K = W, g.N = M.ff, g.epilogue = inner_epilogue, g.out = e->sorted_inter.p;
           RC(gemm_grouped(dtype, g, st));
           g.a = e->sorted_inter.p, g.w = M.down, g.K = M.ff, g.N = W, g.epilogue = 0, g.out = e->pairs_out.p;
           RC(gemm_grouped(dtype, g, st));
         } else {
-          g.a = e->h.p, g.w = M.gate_up, g.a_row_div = M.top, g.K = W, g.N = M.ff, g.epilogue = 1, g.out = e->inter.p;
+          g.a = e->h.p, g.w = M.gate_up, g.a_row_div = M.top, g.K = W, g.N = M.ff, g.epilogue = inner_epilogue, g.out = e->inter.p;
           RC(gemm_grouped(dtype, g, st));
           g.a = e->inter.p, g.w = M.down, g.a_row_div = 1, g.K = M.ff, g.N = W, g.epilogue = 0, g.out = e->pairs_out.p;
           RC(gemm_grouped(dtype, g, st));
@@ -527,11 +685,9 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
         e->mark(KLLM_SEQ_PHASE_SHARED);
       }
       ResidNormArgs a{};
-      a.x = x, a.y1 = y, a.y2 = shared ? y2 : nullptr, a.s2 = shared && M.w_shared_gate ? sgate : nullptr;
-      a.post = nw(L.post_ff), a.T = T, a.width = W, a.dtype = dtype, a.eps = d.norm_eps;
-      if (next_pre.w) a.add = next_add, a.pre = next_pre, a.out = e->h.p, pre_done = true;
-      RC(launch_resid_norm(a, st));
-      e->mark(KLLM_SEQ_PHASE_NORM);
+      a.y1 = y, a.y2 = shared ? y2 : nullptr, a.s2 = shared && M.w_shared_gate ? sgate : nullptr;
+      a.post = nw(L.post_ff);
+      RC(end_of_run(a));
     }
     if (tracing)
       CU(cudaMemcpyAsync(e->trace_host + static_cast<size_t>(r) * T * W, x, Ts * W * 4, cudaMemcpyDeviceToHost, st));
@@ -545,13 +701,14 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
     RC(launch_resid_norm(a, st));
     float* lg = static_cast<float*>(e->logits.p);
     RC(gemm(dtype, e->hw.p, d.head, lg, n_want, W, d.vocab, st));
+    if (d.logit_scale != 0.f && d.logit_scale != 1.f)
+      RC(launch_scale(lg, d.logit_scale, static_cast<size_t>(n_want) * d.vocab, st));
     if (argmax_host) RC(launch_argmax_rows(lg, static_cast<int32_t*>(e->amax.p), n_want, d.vocab, st));
   }
   return 0;
   };  // run_device
 
-  bool all_single = !tracing && e->prof_out == nullptr && e->use_graphs && T <= 32;
-  for (int i = 0; i < n_entries && all_single; ++i) all_single = counts[i] == 1;
+  const bool all_single = single && !tracing && e->prof_out == nullptr && e->use_graphs && T <= 32;
   bool replayed = false;
   if (all_single) {
     const auto key = std::make_tuple(n_entries, n_want, splits, argmax_host ? 1 : 0);

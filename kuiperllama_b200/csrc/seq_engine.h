@@ -27,15 +27,19 @@ constexpr int kAttnThreads = 128;
 struct NormW {
   const float* w;
   const float* b;  // may be null: no bias
+  int kind;        // KLLM_SEQ_NORM_LAYER / KLLM_SEQ_NORM_RMS
 };
 
 // Where the keys and values of one layer run live: pages of `page` tokens, [n_pages][page][kv_heads][dim].
+// k_row / v_row: elements between two tokens' rows (kv_heads * dim and kv_heads * vdim when keys and values have pools
+// of their own; a latent cache keeps one row per token and its values are the head of the key row: v == k, v_row == k_row).
 struct PagedKV {
   void* k;
   void* v;
   const int32_t* table;  // [slots][table_stride]: page number of the i-th page of a sequence
   int table_stride;
   int page;
+  int k_row, v_row;
 };
 
 struct AttnShape {
@@ -45,17 +49,25 @@ struct AttnShape {
   int temp_every;
   int qk_norm;      // RMS norm of each query / key head with a shared weight vector
   int gate;         // one sigmoid gate per (token, head) on the attention output
+  int window;       // position i sees j with 0 <= i - j < window; 0: every earlier position
+  const float* sink;  // [heads] or null: exp(sink) is added to the softmax denominator
+  int q_f32;        // the queries are fp32 whatever the compute type
+  int out_f32;      // the output is written in fp32 whatever the compute type
 };
 
 // ---- seq_kernels.cu -----------------------------------------------------------------------------------------------
-int launch_embed(int dtype, const void* table, const int32_t* tokens, float* x, int T, int width, cudaStream_t s);
+// x[t] = norm(table[tokens[t]]) (norm.w == null: the row itself); `copy` (optional) receives the same rows
+int launch_embed(int dtype, const void* table, const int32_t* tokens, float* x, float* copy, const NormW& norm, float eps,
+                 int T, int width, cudaStream_t s);
 
-// x += LN(y1 + s2[t] * y2; post) (optional; y2 optional);  x += add (a [width] vector, optional);
-// out = LN(x; pre) in the compute type (optional) -- in this order.  `rows` (optional) gathers: row i reads x[rows[i]], and x is then
+// x += N(y1 + s2[t] * y2; post) (optional; y2 optional; post.w == null: the sum itself);  x += add_rows[t];
+// x += add (a [width] vector, optional);  out = N(x; pre) in the compute type (optional) -- in this order.  `rows` (optional) gathers: row i reads x[rows[i]], and x is then
 // left untouched (only `out` is written).
 // Router of a mixture of experts for the rows of `out` (optional, w_router != NULL; needs `pre`): logits z = Wr h in
 // fp32 on the row just written, s = softmax(z), the `top` largest, weights s / (sum + 1e-20) * scale; shared-expert gate
 // sigmoid(w_sg . h) when w_sg is given.
+// kind KLLM_SEQ_ROUTER_SIGMOID: s = sigmoid(z); choice scores s + correction; with groups > 0 only experts of the
+// groups_keep groups with the largest sum of their two best choice scores can be chosen; weights s * scale.
 struct RouterArgs {
   const float* w_router;  // [experts][width]
   const float* w_sg;      // [width] or NULL
@@ -64,6 +76,18 @@ struct RouterArgs {
   int32_t* top_idx;       // [T, top]
   float* top_w;           // [T, top]
   float* sgate;           // [T]
+  int kind;
+  const float* correction;  // [experts] or NULL
+  int groups, groups_keep;
+};
+__host__ __device__ inline size_t router_smem_floats(const RouterArgs& r) { return 2 * static_cast<size_t>(r.experts) + r.groups; }
+// Token shift on the rows a norm kernel writes, for steps in which every sequence brings ONE token: the row's CTA owns
+// its sequence's state.  out = h + (prev - h) * mu, prev = state[seq] (zeros at position 0); state[seq] = h.
+struct ShiftArgs {
+  const float* mu;     // [width] or null: no shift
+  float* state;        // [slots][width]
+  const int32_t* tok_seq;
+  const int32_t* tok_pos;
 };
 struct ResidNormArgs {
   float* x;
@@ -78,6 +102,9 @@ struct ResidNormArgs {
   int T, width, dtype;
   float eps;
   RouterArgs router;
+  const float* add_rows;  // [T, width] added to x row by row (before `add`), optional
+  float* out_f32;         // instead of `out`: the normed rows in fp32 (a token-shift kernel follows)
+  ShiftArgs shift;        // inline token shift (single-token steps)
 };
 int launch_resid_norm(const ResidNormArgs& a, cudaStream_t s);
 
@@ -103,6 +130,43 @@ int launch_attention_mma(const AttnShape& a, const void* q, const float* gates, 
                          const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
                          const int32_t* ent_pos0, int max_count, int splits, float* ws, void* out, cudaStream_t s);
 
+// Token shift for steps with longer entries: out[t] = h[t] + (prev - h[t]) * mu in the compute type, prev = h[t - 1] inside
+// an entry, the sequence's state (zeros at position 0) for its first row; afterwards state[seq] = the entry's last h.
+int launch_token_shift(int dtype, const float* h, const float* mu, float* state, const int32_t* tok_seq,
+                       const int32_t* tok_pos, const int32_t* ent_first, const int32_t* ent_count, int n_entries, void* out,
+                       int T, int width, cudaStream_t s);
+
+// ---- seq_mixers.cu: attention through a latent, linear attention, dense feed-forward activations -----------------------
+struct LatentShape {
+  int heads, dim, rot_dim, vdim, q_rank, kv_rank;
+  int rope_dims;
+  float rope_base;
+};
+// proj [T, q_rank + kv_rank + rot_dim + heads] fp32 -> cq [T, q_rank] (compute type, RMS-normed), the cache row
+// [kv_rank normed latent | rot_dim rotated key part] of every token, gates [T, heads] = sigmoid
+int launch_latent_prepare(int dtype, const LatentShape& a, const float* proj, const float* q_norm_w, const float* kv_norm_w,
+                          float eps, const int32_t* tok_seq, const int32_t* tok_pos, void* cq, float* gates,
+                          const PagedKV& kv, int T, cudaStream_t s);
+// q [T, heads, dim + rot_dim] fp32 -> qa [T, heads, kv_rank + rot_dim] fp32: W_uk(head)^T q_plain | rotated q_rot
+int launch_latent_absorb(int dtype, const LatentShape& a, const float* q, const void* w_uk, const int32_t* tok_pos, float* qa,
+                         int T, cudaStream_t s);
+// ol [T, heads, kv_rank] fp32 (weighted sums of latents) -> out [T, heads * vdim] compute type: W_uv(head) ol
+int launch_latent_expand(int dtype, const LatentShape& a, const float* ol, const void* w_uv, void* out, int T, cudaStream_t s);
+
+// proj [T, 2 * heads * dim + 2 * heads * vdim] fp32: q | k | v | gate rows before their activations.  Runs the recurrence
+// of every entry from its sequence's state ([slots][heads][dim][vdim] fp32; zeros at position 0), writes o [T, heads * vdim]
+// fp32 and the new state.
+int launch_linear_attention(int heads, int dim, int vdim, const float* decay, const float* proj, float* state, int n_entries,
+                            const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
+                            const int32_t* ent_pos0, int max_count, float* o, cudaStream_t s);
+// out[t] = RMSnorm(o[t]; w) * sigmoid(gate rows of proj[t]) in the compute type
+int launch_linear_out(int dtype, int heads, int dim, int vdim, const float* o, const float* proj, const float* norm_w, float eps,
+                      void* out, int T, cudaStream_t s);
+// out = act(z) element by element (z fp32 [n], out compute type): KLLM_SEQ_ACT_XIELU with (a, b), or KLLM_SEQ_ACT_RELU2
+int launch_activation(int dtype, int act, float a, float b, const float* z, void* out, size_t n, cudaStream_t s);
+// v *= scale
+int launch_scale(float* v, float scale, size_t n, cudaStream_t s);
+
 // Router: z = Wr h (fp32), s = softmax(z), the `top` largest, weights s / (sum + 1e-20) * scale; shared-expert gate
 // sigmoid(w_sg . h) when w_sg is given.
 int launch_router(int dtype, const void* h, const float* w_router, const float* w_sg, int experts, int top,
@@ -121,8 +185,9 @@ struct SharedExpert {
   int ff;               // 0: no shared expert in these kernels
 };
 bool shared_expert_rides_along(int top, int ff, int shared_ff);
+// act KLLM_SEQ_ACT_RELU2: inter[pair] = max(Wu h, 0)^2 with gate_up = [experts][ff][width] (no shared expert then)
 int launch_expert_gate_up(int dtype, const void* h, const void* gate_up, const int32_t* top_idx, void* inter, int T,
-                          int top, int ff, int width, const SharedExpert& sh, cudaStream_t s);
+                          int top, int ff, int width, const SharedExpert& sh, int act, cudaStream_t s);
 int launch_expert_down(int dtype, const void* inter, const void* down, const int32_t* top_idx, const float* top_w,
                        float* y, int T, int top, int ff, int width, const SharedExpert& sh, cudaStream_t s);
 
@@ -152,7 +217,7 @@ struct GroupedArgs {
   int a_row_div;            // row of `a` for pair p is p / a_row_div (gate_up: top; down: 1)
   int n_blocks, block, K, N;
   // epilogue: 0 = out[pair, n] = acc (fp32);  1 = out[pair, f] = silu(acc_gate) * acc_up in the compute type (the
-  // weights hold ff gate rows, then ff up rows; N = ff)
+  // weights hold ff gate rows, then ff up rows; N = ff);  2 = out[pair, f] = max(acc, 0)^2 in the compute type
   int epilogue;
   void* out;
   // tensor-core form (bf16): `a` is already in sorted order [n_blocks * block, K] and epilogue 1 writes its result in

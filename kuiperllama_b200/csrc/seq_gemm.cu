@@ -108,7 +108,8 @@ rows_kernel(const AT* __restrict__ a, const AT* __restrict__ w, float* __restric
 constexpr int TM = 64, TN = 64, TK = 16;
 
 // GROUPED: row i of block b is pair sorted_pair[b * TM + i] (or -1); its `a` row is pair / a_row_div, the weights are
-// those of expert block_expert[b].  EPI 1 computes gate and up together (weights: ff gate rows then ff up rows).
+// those of expert block_expert[b].  EPI 1 computes gate and up together (weights: ff gate rows then ff up rows); EPI 2
+// squares the positive part of a single product.
 template <typename AT, bool GROUPED, int EPI>
 __global__ void __launch_bounds__(256)
 tiled_kernel(const AT* __restrict__ a, const AT* __restrict__ w, void* __restrict__ out_, int T, int K, int N,
@@ -188,6 +189,9 @@ tiled_kernel(const AT* __restrict__ a, const AT* __restrict__ w, void* __restric
       if (EPI == 1) {
         const float g = acc[0][i][j], u = acc[EPI == 1 ? 1 : 0][i][j];
         st_t(static_cast<AT*>(out_) + static_cast<size_t>(dst) * N + n, g / (1.0f + expf(-g)) * u);
+      } else if (EPI == 2) {
+        const float u = fmaxf(acc[0][i][j], 0.f);
+        st_t(static_cast<AT*>(out_) + static_cast<size_t>(dst) * N + n, u * u);
       } else {
         static_cast<float*>(out_)[static_cast<size_t>(dst) * N + n] = acc[0][i][j];
       }
@@ -232,6 +236,9 @@ int grouped_t(const GroupedArgs& g, cudaStream_t s) {
   if (g.epilogue == 1)
     tiled_kernel<AT, true, 1><<<grid, 256, 0, s>>>(static_cast<const AT*>(g.a), static_cast<const AT*>(g.w), g.out, 0, g.K,
                                                   g.N, g.sorted_pair, g.block_expert, g.a_row_div);
+  else if (g.epilogue == 2)
+    tiled_kernel<AT, true, 2><<<grid, 256, 0, s>>>(static_cast<const AT*>(g.a), static_cast<const AT*>(g.w), g.out, 0, g.K,
+                                                  g.N, g.sorted_pair, g.block_expert, g.a_row_div);
   else
     tiled_kernel<AT, true, 0><<<grid, 256, 0, s>>>(static_cast<const AT*>(g.a), static_cast<const AT*>(g.w), g.out, 0, g.K,
                                                   g.N, g.sorted_pair, g.block_expert, g.a_row_div);
@@ -274,6 +281,8 @@ int gemm_grouped(int dtype, const GroupedArgs& g, cudaStream_t s) {
     g_umma_used = true;
     if (g.epilogue == 1)
       return umma::launch_grouped<1>(g.a, g.w, g.out, g.sorted_pair, g.block_expert, g.n_blocks, g.experts, g.K, g.N, s);
+    if (g.epilogue == 2)
+      return umma::launch_grouped<2>(g.a, g.w, g.out, g.sorted_pair, g.block_expert, g.n_blocks, g.experts, g.K, g.N, s);
     return umma::launch_grouped<0>(g.a, g.w, g.out, g.sorted_pair, g.block_expert, g.n_blocks, g.experts, g.K, g.N, s);
   }
   if (dtype == KLLM_SEQ_F32) return grouped_t<float>(g, s);

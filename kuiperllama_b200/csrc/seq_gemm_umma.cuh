@@ -207,6 +207,7 @@ umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
 // EPI 1: the weights of an expert are N gate rows followed by N up rows; both accumulate side by side in TMEM and
 //        out[block row, n] = silu(gate) * up in bf16, still in sorted order (the next product reads it as its `a`).
 // EPI 0: out[pair, n] = acc in fp32, pair = sorted_pair[block row] (rows of padding are skipped).
+// EPI 2: one product; max(acc, 0)^2 in bf16, written in sorted order like EPI 1.
 constexpr int GBN = 64;
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -306,6 +307,9 @@ umma_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
               const float g = __uint_as_float(r[j]), up = __uint_as_float(u[j]);
               static_cast<__nv_bfloat16*>(out_)[static_cast<size_t>(br) * N + row] =
                   __float2bfloat16_rn(g / (1.0f + expf(-g)) * up);
+            } else if (EPI == 2) {
+              const float up = fmaxf(__uint_as_float(r[j]), 0.f);
+              static_cast<__nv_bfloat16*>(out_)[static_cast<size_t>(br) * N + row] = __float2bfloat16_rn(up * up);
             } else {
               const int pair = sorted_pair[br];
               if (pair >= 0) static_cast<float*>(out_)[static_cast<size_t>(pair) * N + row] = __uint_as_float(r[j]);

@@ -132,12 +132,47 @@ __device__ __forceinline__ void warp_dot2(const AT* __restrict__ w0, const AT* _
 }
 
 // ---- embedding ----------------------------------------------------------------------------------------------------
+// mean and 1 / sqrt(var + eps) of a row in shared memory (layer norm), or 0 and 1 / sqrt(mean square + eps) (RMS norm)
+__device__ __forceinline__ void row_stats(const float* buf, int W, int kind, float eps, float* red, float& mean, float& rstd) {
+  const float inv_w = 1.0f / static_cast<float>(W);
+  mean = 0.f;
+  if (kind == KLLM_SEQ_NORM_LAYER) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) s += buf[i];
+    mean = block_sum(s, red) * inv_w;
+  }
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float d = buf[i] - mean;
+    q += d * d;
+  }
+  rstd = 1.0f / sqrtf(block_sum(q, red) * inv_w + eps);
+}
+
 template <typename AT>
 __global__ void embed_kernel(const AT* __restrict__ table, const int32_t* __restrict__ tokens, float* __restrict__ x,
-                             int width) {
+                             float* __restrict__ copy, NormW norm, float eps, int width) {
+  extern __shared__ float buf[];
+  __shared__ float red[33];
   const int t = blockIdx.x;
   const AT* row = table + static_cast<size_t>(tokens[t]) * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) x[static_cast<size_t>(t) * width + i] = to_f(row[i]);
+  if (norm.w == nullptr) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      const float v = to_f(row[i]);
+      x[static_cast<size_t>(t) * width + i] = v;
+      if (copy) copy[static_cast<size_t>(t) * width + i] = v;
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < width; i += blockDim.x) buf[i] = to_f(row[i]);
+  __syncthreads();
+  float mean, rstd;
+  row_stats(buf, width, norm.kind, eps, red, mean, rstd);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = (buf[i] - mean) * rstd * norm.w[i] + (norm.b ? norm.b[i] : 0.f);
+    x[static_cast<size_t>(t) * width + i] = v;
+    if (copy) copy[static_cast<size_t>(t) * width + i] = v;
+  }
 }
 
 // ---- router ---------------------------------------------------------------------------------------------------------
@@ -156,6 +191,72 @@ __device__ void route_token(const RouterArgs& r, const float* xs, float* z, int 
   }
   __syncthreads();
   if (warp != 0) return;
+  if (r.kind == KLLM_SEQ_ROUTER_SIGMOID) {
+    // z: scores s;  c: choice scores (s + correction, -inf outside the kept groups and once chosen);  gs: group scores
+    float* c = z + experts;
+    float* gs = c + experts;
+    for (int e = lane; e < experts; e += 32) {
+      const float sc = 1.0f / (1.0f + expf(-z[e]));
+      z[e] = sc;
+      c[e] = sc + (r.correction ? r.correction[e] : 0.f);
+    }
+    __syncwarp();
+    if (r.groups > 0) {
+      const int size = experts / r.groups;
+      for (int g = lane; g < r.groups; g += 32) {
+        float b0 = -INFINITY, b1 = -INFINITY;
+        for (int i = 0; i < size; ++i) {
+          const float v = c[g * size + i];
+          if (v > b0) b1 = b0, b0 = v;
+          else if (v > b1) b1 = v;
+        }
+        gs[g] = size > 1 ? b0 + b1 : b0;
+      }
+      __syncwarp();
+      // the groups_keep best groups keep their scores (marked by +inf in gs); the others' experts drop out
+      for (int k = 0; k < r.groups_keep; ++k) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int g = lane; g < r.groups; g += 32) {
+          const float v = gs[g];
+          if (v != INFINITY && (v > best || bi == 0x7fffffff)) best = v, bi = g;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(kAll, best, o);
+          const int oi = __shfl_xor_sync(kAll, bi, o);
+          if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) best = ob, bi = oi;
+        }
+        if (lane == 0 && bi != 0x7fffffff) gs[bi] = INFINITY;
+        __syncwarp();
+      }
+      for (int e = lane; e < experts; e += 32)
+        if (gs[e / size] != INFINITY) c[e] = -INFINITY;
+      __syncwarp();
+    }
+    for (int k = 0; k < top; ++k) {
+      float best = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int e = lane; e < experts; e += 32) {
+        const float v = c[e];
+        if (v > best) best = v, bi = e;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(kAll, best, o);
+        const int oi = __shfl_xor_sync(kAll, bi, o);
+        if (ob > best || (ob == best && oi < bi)) best = ob, bi = oi;
+      }
+      if (bi == 0x7fffffff) bi = 0;  // fewer eligible experts than `top`: a configuration error, kept in range
+      if (lane == 0) {
+        r.top_idx[static_cast<size_t>(t) * top + k] = bi;
+        r.top_w[static_cast<size_t>(t) * top + k] = z[bi] * r.scale;
+        c[bi] = -INFINITY;
+      }
+      __syncwarp();
+    }
+    return;
+  }
   float mx = -INFINITY;
   for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
   mx = warp_max(mx);
@@ -197,9 +298,9 @@ __device__ void route_token(const RouterArgs& r, const float* xs, float* z, int 
 
 template <typename AT>
 __global__ void router_kernel(const AT* __restrict__ h, RouterArgs r, int width) {
-  extern __shared__ float sm[];  // [experts] logits, then [width] the token's row in fp32
+  extern __shared__ float sm[];  // the router's scratch, then [width] the token's row in fp32
   float* z = sm;
-  float* xs = sm + r.experts;
+  float* xs = sm + router_smem_floats(r);
   const int t = blockIdx.x;
   const AT* x = h + static_cast<size_t>(t) * width;
   for (int k = threadIdx.x; k < width; k += blockDim.x) xs[k] = to_f(x[k]);
@@ -207,38 +308,34 @@ __global__ void router_kernel(const AT* __restrict__ h, RouterArgs r, int width)
   route_token(r, xs, z, t, width);
 }
 
-// ---- residual + layer norms ---------------------------------------------------------------------------------------
-// Layer norm as the model family defines it: (v - mean) / sqrt(var + eps) * w + b, var = mean of squared deviations.
+// ---- residual + norms -----------------------------------------------------------------------------------------------
+// Layer norm: (v - mean) / sqrt(var + eps) * w + b, var = mean of squared deviations.  RMS norm: v / sqrt(mean(v^2) + eps) * w.
 template <typename AT>
 __global__ void resid_norm_kernel(ResidNormArgs a) {
-  extern __shared__ float buf[];  // [width], then [experts] when the kernel also routes
+  extern __shared__ float buf[];  // [width], then the router's scratch when the kernel also routes
   __shared__ float red[33];
   const int W = a.width;
   const int r = blockIdx.x;
   const size_t src = static_cast<size_t>(a.rows ? a.rows[r] : r) * W;
   const size_t dst = static_cast<size_t>(r) * W;
-  const float inv_w = 1.0f / static_cast<float>(W);
-  const bool has_post = a.post.w != nullptr;
-  if (has_post) {
-    float s = 0.f;
+  const bool changes = a.y1 != nullptr || a.add != nullptr || a.add_rows != nullptr;
+  if (a.y1 != nullptr) {
     const float g = a.s2 ? a.s2[r] : 1.0f;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
-      float u = a.y1 ? a.y1[src + i] : 0.f;
+      float u = a.y1[src + i];
       if (a.y2) u += g * a.y2[src + i];
       buf[i] = u;
-      s += u;
     }
-    const float mean = block_sum(s, red) * inv_w;
-    float q = 0.f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-      const float d = buf[i] - mean;
-      q += d * d;
+    float mean = 0.f, rstd = 1.f;
+    if (a.post.w != nullptr) {
+      __syncthreads();
+      row_stats(buf, W, a.post.kind, a.eps, red, mean, rstd);
     }
-    const float var = block_sum(q, red) * inv_w;
-    const float rstd = 1.0f / sqrtf(var + a.eps);
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
       float v = a.x[src + i];
-      v += (buf[i] - mean) * rstd * a.post.w[i] + (a.post.b ? a.post.b[i] : 0.f);
+      if (a.post.w != nullptr) v += (buf[i] - mean) * rstd * a.post.w[i] + (a.post.b ? a.post.b[i] : 0.f);
+      else v += buf[i];
+      if (a.add_rows) v += a.add_rows[src + i];
       if (a.add) v += a.add[i];
       buf[i] = v;
       if (!a.rows) a.x[dst + i] = v;
@@ -246,34 +343,71 @@ __global__ void resid_norm_kernel(ResidNormArgs a) {
   } else {
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
       float v = a.x[src + i];
-      if (a.add) {
-        v += a.add[i];
-        if (!a.rows) a.x[dst + i] = v;
-      }
+      if (a.add_rows) v += a.add_rows[src + i];
+      if (a.add) v += a.add[i];
+      if (changes && !a.rows) a.x[dst + i] = v;
       buf[i] = v;
     }
   }
   if (a.pre.w == nullptr) return;
-  float s = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) s += buf[i];
-  const float mean = block_sum(s, red) * inv_w;
-  float q = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float d = buf[i] - mean;
-    q += d * d;
-  }
-  const float var = block_sum(q, red) * inv_w;
-  const float rstd = 1.0f / sqrtf(var + a.eps);
-  AT* out = static_cast<AT*>(a.out) + dst;
+  __syncthreads();
+  float mean, rstd;
+  row_stats(buf, W, a.pre.kind, a.eps, red, mean, rstd);
   const bool route = a.router.w_router != nullptr;
+  if (a.out_f32 != nullptr) {  // fp32 rows for a token-shift kernel
+    for (int i = threadIdx.x; i < W; i += blockDim.x)
+      a.out_f32[dst + i] = (buf[i] - mean) * rstd * a.pre.w[i] + (a.pre.b ? a.pre.b[i] : 0.f);
+    return;
+  }
+  AT* out = static_cast<AT*>(a.out) + dst;
+  float* state = nullptr;
+  bool first = true;
+  if (a.shift.mu != nullptr) {
+    state = a.shift.state + static_cast<size_t>(a.shift.tok_seq[r]) * W;
+    first = a.shift.tok_pos[r] == 0;
+  }
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const AT o = from_f<AT>((buf[i] - mean) * rstd * a.pre.w[i] + (a.pre.b ? a.pre.b[i] : 0.f));
+    float h = (buf[i] - mean) * rstd * a.pre.w[i] + (a.pre.b ? a.pre.b[i] : 0.f);
+    if (state != nullptr) {
+      const float prev = first ? 0.f : state[i];
+      state[i] = h;
+      h = h + (prev - h) * a.shift.mu[i];
+    }
+    const AT o = from_f<AT>(h);
     out[i] = o;
     if (route) buf[i] = to_f(o);  // the router reads what the experts read: the row in the compute type
   }
   if (!route) return;
   __syncthreads();
   route_token(a.router, buf, buf + W, r, W);
+}
+
+// One CTA per row; the CTA of an entry's first row also moves the entry's last h into the state (it alone touches it).
+template <typename AT>
+__global__ void token_shift_kernel(const float* __restrict__ h, const float* __restrict__ mu, float* __restrict__ state,
+                                   const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos,
+                                   const int32_t* __restrict__ ent_first, const int32_t* __restrict__ ent_count,
+                                   int n_entries, AT* __restrict__ out, int W) {
+  const int t = blockIdx.x;
+  // the entry of this row: entries are few, rows of an entry are consecutive
+  int e = 0;
+  while (e + 1 < n_entries && ent_first[e + 1] <= t) ++e;
+  const bool first_row = ent_first[e] == t;
+  const float* cur = h + static_cast<size_t>(t) * W;
+  float* st = state + static_cast<size_t>(tok_seq[t]) * W;
+  const float* last = h + static_cast<size_t>(ent_first[e] + ent_count[e] - 1) * W;
+  const bool start = tok_pos[t] == 0;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float prev;
+    if (first_row) {
+      prev = start ? 0.f : st[i];
+      st[i] = last[i];
+    } else {
+      prev = cur[i - W];
+    }
+    const float v = cur[i];
+    out[static_cast<size_t>(t) * W + i] = from_f<AT>(v + (prev - v) * mu[i]);
+  }
 }
 
 // ---- query / key preparation ----------------------------------------------------------------------------------------
@@ -335,7 +469,7 @@ __global__ void qk_prepare_kernel(AttnShape a, const float* __restrict__ qkvg, c
 // the unrolled row loops do not issue twelve predicated-off iterations per step.
 template <typename AT, int C, bool SPARSE, int RS>
 __global__ void __launch_bounds__(kAttnThreads)
-attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_t* __restrict__ ent_first,
+attention_kernel(AttnShape a, const void* __restrict__ q_, PagedKV kv, const int32_t* __restrict__ ent_first,
                  const int32_t* __restrict__ ent_count, const int32_t* __restrict__ ent_seq,
                  const int32_t* __restrict__ ent_pos0, int splits, float* __restrict__ ws) {
   const int e = blockIdx.y / a.kv_heads, g = blockIdx.y % a.kv_heads, split = blockIdx.z;
@@ -347,8 +481,10 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
   const int rows_here = min(kAttnRows, n_rows - r0);
   const int pmax = pos0 + (r0 + rows_here - 1) / rep;  // last position any row of the tile sees
   const int n_tiles = pmax / kAttnKeys + 1;
-  const int per = (n_tiles + splits - 1) / splits;
-  const int tile_lo = split * per, tile_hi = min(n_tiles, tile_lo + per);
+  // with a window the first row of the tile sees nothing before its position - window + 1
+  const int tile_first = a.window > 0 ? max(0, pos0 + r0 / rep - a.window + 1) / kAttnKeys : 0;
+  const int per = (n_tiles - tile_first + splits - 1) / splits;
+  const int tile_lo = tile_first + split * per, tile_hi = min(n_tiles, tile_lo + per);
 
   const int dq = (a.dim + 3) & ~3, dk = dq + 1;
   extern __shared__ float sm[];
@@ -368,7 +504,8 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
     if (r < rows_here && d < a.dim) {
       const int rr = r0 + r;
       const int t = first + rr / rep, h = g * rep + rr % rep;
-      v = to_f(q[(static_cast<size_t>(t) * a.heads + h) * a.dim + d]) * a.scale;
+      const size_t qi = (static_cast<size_t>(t) * a.heads + h) * a.dim + d;
+      v = (a.q_f32 ? static_cast<const float*>(q_)[qi] : to_f(static_cast<const AT*>(q_)[qi])) * a.scale;
     }
     Qs[i] = v;
   }
@@ -389,7 +526,8 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
   const AT* kbase = static_cast<const AT*>(kv.k);
   const AT* vbase = static_cast<const AT*>(kv.v);
   const int32_t* table = kv.table + static_cast<size_t>(seq) * kv.table_stride;
-  const bool vec_tiles = SPARSE && (a.dim % VecOf<AT>::N) == 0 && (a.vdim % VecOf<AT>::N) == 0;
+  const bool vec_tiles = SPARSE && (a.dim % VecOf<AT>::N) == 0 && (a.vdim % VecOf<AT>::N) == 0 &&
+                         (kv.k_row % VecOf<AT>::N) == 0 && (kv.v_row % VecOf<AT>::N) == 0;
   // Rows of this thread: thread group rg takes rows rg * rpt .. rg * rpt + my_rows - 1.  A full tile gives each of the
   // two groups 16 rows; a SPARSE tile (a decode step fills only heads / kv_heads rows) splits the rows that exist
   // between the groups, so both halves of the CTA work.
@@ -418,8 +556,8 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
             const int kj = k0 + j;
             if (kj <= pmax) {
               const size_t slot = static_cast<size_t>(table[kj / kv.page]) * kv.page + kj % kv.page;
-              if (c < kc) VecOf<AT>::load(kbase + (slot * a.kv_heads + g) * a.dim + c * V, f[u]);
-              else VecOf<AT>::load(vbase + (slot * a.kv_heads + g) * a.vdim + (c - kc) * V, f[u]);
+              if (c < kc) VecOf<AT>::load(kbase + slot * kv.k_row + g * a.dim + c * V, f[u]);
+              else VecOf<AT>::load(vbase + slot * kv.v_row + g * a.vdim + (c - kc) * V, f[u]);
             }
           }
         }
@@ -444,8 +582,8 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
       float* vd = Vs + j * a.vdim;
       if (kj <= pmax) {
         const size_t slot = static_cast<size_t>(table[kj / kv.page]) * kv.page + kj % kv.page;
-        const AT* ksrc = kbase + (slot * a.kv_heads + g) * a.dim;
-        const AT* vsrc = vbase + (slot * a.kv_heads + g) * a.vdim;
+        const AT* ksrc = kbase + slot * kv.k_row + g * a.dim;
+        const AT* vsrc = vbase + slot * kv.v_row + g * a.vdim;
         for (int d = lane; d < dk; d += 32) kd[d] = d < a.dim ? to_f(ksrc[d]) : 0.f;
         for (int d = lane; d < a.vdim; d += 32) vd[d] = to_f(vsrc[d]);
       } else {
@@ -477,7 +615,8 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
       for (int i = 0; i < RPT; ++i) {
         if (SPARSE && i >= my_rows) break;  // the softmax below reads only rows that exist
         const int r = rg * rpt + i;
-        const bool visible = r < rows_here && kj <= pos0 + (r0 + r) / rep;
+        const int pr = pos0 + (r0 + r) / rep;
+        const bool visible = r < rows_here && kj <= pr && (a.window == 0 || pr - kj < a.window);
         Ss[r * kAttnKeys + key] = visible ? sc[i] : -INFINITY;
       }
     }
@@ -555,13 +694,14 @@ attention_kernel(AttnShape a, const AT* __restrict__ q, PagedKV kv, const int32_
 
 template <typename AT>
 __global__ void attention_merge_kernel(int heads, int vdim, int splits, const float* __restrict__ ws,
-                                       const float* __restrict__ gates, AT* __restrict__ out) {
+                                       const float* __restrict__ gates, const float* __restrict__ sink, int out_f32,
+                                       void* __restrict__ out_) {
   const size_t th = blockIdx.x;  // t * heads + h
   const int pstride = vdim + 2;
   const float* p = ws + th * splits * pstride;
-  float M = -INFINITY;
+  float M = sink ? sink[th % heads] : -INFINITY;
   for (int s = 0; s < splits; ++s) M = fmaxf(M, p[s * pstride]);
-  float L = 0.f;
+  float L = sink ? expf(sink[th % heads] - M) : 0.f;
   for (int s = 0; s < splits; ++s) {
     const float m = p[s * pstride];
     if (m > -INFINITY) L += p[s * pstride + 1] * expf(m - M);
@@ -573,7 +713,8 @@ __global__ void attention_merge_kernel(int heads, int vdim, int splits, const fl
       const float m = p[s * pstride];
       if (m > -INFINITY) o += p[s * pstride + 2 + d] * expf(m - M);
     }
-    out[th * vdim + d] = from_f<AT>(o / L * gate);
+    if (out_f32) static_cast<float*>(out_)[th * vdim + d] = o / L * gate;
+    else static_cast<AT*>(out_)[th * vdim + d] = from_f<AT>(o / L * gate);
   }
 }
 
@@ -586,7 +727,7 @@ __host__ __device__ inline int pair_rows(int pairs) { return pairs <= 32 ? 4 : 1
 template <typename AT>
 __global__ void expert_gate_up_kernel(const AT* __restrict__ h, const AT* __restrict__ gate_up,
                                       const int32_t* __restrict__ top_idx, AT* __restrict__ inter, int T, int top, int ff,
-                                      int width, SharedExpert sh) {
+                                      int width, SharedExpert sh, int act) {
   extern __shared__ float xs[];  // [width]
   const int pair = blockIdx.x;
   const bool is_shared = pair >= T * top;
@@ -598,11 +739,18 @@ __global__ void expert_gate_up_kernel(const AT* __restrict__ h, const AT* __rest
   for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(h[static_cast<size_t>(t) * width + i]);
   __syncthreads();
   const AT* wg = is_shared ? static_cast<const AT*>(sh.gate_up)
-                           : gate_up + static_cast<size_t>(top_idx[pair]) * 2 * ff * width;
+                           : gate_up + static_cast<size_t>(top_idx[pair]) * (act == KLLM_SEQ_ACT_SWIGLU ? 2 : 1) * ff * width;
   const AT* wu = wg + static_cast<size_t>(rows) * width;
   AT* dst = is_shared ? static_cast<AT*>(sh.inter) + static_cast<size_t>(t) * sh.ff
                       : inter + static_cast<size_t>(pair) * ff;
   const int f_end = min(rows, (blockIdx.y + 1) * kPairRows);
+  if (act == KLLM_SEQ_ACT_RELU2) {
+    for (int f = blockIdx.y * kPairRows + warp; f < f_end; f += nw) {
+      const float uv = fmaxf(warp_dot(wg + static_cast<size_t>(f) * width, xs, width, lane), 0.f);
+      if (lane == 0) dst[f] = from_f<AT>(uv * uv);
+    }
+    return;
+  }
   for (int f = blockIdx.y * kPairRows + warp; f < f_end; f += nw) {
     float gv, uv;
     warp_dot2(wg + static_cast<size_t>(f) * width, wu + static_cast<size_t>(f) * width, xs, width, lane, gv, uv);
@@ -753,13 +901,25 @@ inline int done() {
 
 }  // namespace
 
-int launch_embed(int dtype, const void* table, const int32_t* tokens, float* x, int T, int width, cudaStream_t s) {
-  KLLM_SEQ_DISPATCH(dtype, (embed_kernel<AT><<<T, 128, 0, s>>>(static_cast<const AT*>(table), tokens, x, width)));
+int launch_embed(int dtype, const void* table, const int32_t* tokens, float* x, float* copy, const NormW& norm, float eps,
+                 int T, int width, cudaStream_t s) {
+  const size_t smem = static_cast<size_t>(width) * sizeof(float);
+  if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
+  KLLM_SEQ_DISPATCH(dtype, (embed_kernel<AT><<<T, 128, smem, s>>>(static_cast<const AT*>(table), tokens, x, copy, norm, eps,
+                                                                 width)));
+  return done();
+}
+
+int launch_token_shift(int dtype, const float* h, const float* mu, float* state, const int32_t* tok_seq,
+                       const int32_t* tok_pos, const int32_t* ent_first, const int32_t* ent_count, int n_entries, void* out,
+                       int T, int width, cudaStream_t s) {
+  KLLM_SEQ_DISPATCH(dtype, (token_shift_kernel<AT><<<T, 128, 0, s>>>(h, mu, state, tok_seq, tok_pos, ent_first, ent_count,
+                                                                    n_entries, static_cast<AT*>(out), width)));
   return done();
 }
 
 int launch_resid_norm(const ResidNormArgs& a, cudaStream_t s) {
-  const size_t smem = (static_cast<size_t>(a.width) + (a.router.w_router ? a.router.experts : 0)) * sizeof(float);
+  const size_t smem = (static_cast<size_t>(a.width) + (a.router.w_router ? router_smem_floats(a.router) : 0)) * sizeof(float);
   if (smem > 200 * 1024) return KLLM_E_UNSUPPORTED;
   if (a.router.w_router && (a.router.top > a.router.experts || a.router.experts <= 0 || a.router.top <= 0 || !a.pre.w))
     return KLLM_E_INVALID;
@@ -803,8 +963,8 @@ static int launch_attention_cs(const AttnShape& a, const void* q, const PagedKV&
   }
   const int rep = a.heads / a.kv_heads;
   const dim3 grid((max_count * rep + kAttnRows - 1) / kAttnRows, n_entries * a.kv_heads, splits);
-  attention_kernel<AT, C, SPARSE, RS><<<grid, kAttnThreads, smem, s>>>(a, static_cast<const AT*>(q), kv, ent_first, ent_count,
-                                                          ent_seq, ent_pos0, splits, ws);
+  attention_kernel<AT, C, SPARSE, RS><<<grid, kAttnThreads, smem, s>>>(a, q, kv, ent_first, ent_count, ent_seq, ent_pos0, splits,
+                                                                       ws);
   return done();
 }
 
@@ -849,17 +1009,17 @@ int launch_attention(int dtype, const AttnShape& a, const void* q, const float* 
   }
   if (rc) return rc;
   KLLM_SEQ_DISPATCH(dtype, (attention_merge_kernel<AT><<<T * a.heads, 64, 0, s>>>(a.heads, a.vdim, splits, ws,
-                                                                                 a.gate ? gates : nullptr,
-                                                                                 static_cast<AT*>(out))));
+                                                                                 a.gate ? gates : nullptr, a.sink, a.out_f32,
+                                                                                 out)));
   return done();
 }
 
 int launch_router(int dtype, const void* h, const float* w_router, const float* w_sg, int experts, int top,
                   float scale, int32_t* top_idx, float* top_w, float* sgate, int T, int width, cudaStream_t s) {
   if (top > experts || experts <= 0 || top <= 0) return KLLM_E_INVALID;
-  const size_t smem = (static_cast<size_t>(experts) + width) * sizeof(float);
+  const RouterArgs r{w_router, w_sg, experts, top, scale, top_idx, top_w, sgate, KLLM_SEQ_ROUTER_SOFTMAX, nullptr, 0, 0};
+  const size_t smem = (router_smem_floats(r) + width) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
-  const RouterArgs r{w_router, w_sg, experts, top, scale, top_idx, top_w, sgate};
   KLLM_SEQ_DISPATCH(dtype, (router_kernel<AT><<<T, 256, smem, s>>>(static_cast<const AT*>(h), r, width)));
   return done();
 }
@@ -869,7 +1029,8 @@ bool shared_expert_rides_along(int top, int ff, int shared_ff) {
 }
 
 int launch_expert_gate_up(int dtype, const void* h, const void* gate_up, const int32_t* top_idx, void* inter, int T,
-                          int top, int ff, int width, const SharedExpert& sh, cudaStream_t s) {
+                          int top, int ff, int width, const SharedExpert& sh, int act, cudaStream_t s) {
+  if (act != KLLM_SEQ_ACT_SWIGLU && (act != KLLM_SEQ_ACT_RELU2 || sh.ff > 0)) return KLLM_E_UNSUPPORTED;
   const size_t smem = static_cast<size_t>(width) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
   const int kPairRows = pair_rows(T * top);
@@ -877,7 +1038,7 @@ int launch_expert_gate_up(int dtype, const void* h, const void* gate_up, const i
   KLLM_SEQ_DISPATCH(dtype, (expert_gate_up_kernel<AT><<<grid, 128, smem, s>>>(static_cast<const AT*>(h),
                                                                              static_cast<const AT*>(gate_up), top_idx,
                                                                              static_cast<AT*>(inter), T, top, ff, width,
-                                                                             sh)));
+                                                                             sh, act)));
   return done();
 }
 

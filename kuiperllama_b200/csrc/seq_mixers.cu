@@ -1,0 +1,363 @@
+// Kernels of the mixers that keep something other than per-head keys and values, and of the dense feed-forward:
+//
+//   attention through a latent   latent_prepare (RMS norms of the two down-projections, rotation of the shared key part,
+//                                scatter of [latent | rotated part] into the pages, gates), latent_absorb (a head's plain
+//                                query dimensions carried into the latent space, W_uk^T q, and the rotation of its rotated
+//                                dimensions), latent_expand (W_uv on the weighted sum of latents).  Between absorb and expand
+//                                the paged attention kernel of seq_kernels.cu runs with one key/value "head" of
+//                                kv_rank + rot_dim key and kv_rank value dimensions that every query head shares.
+//   linear attention             the decayed-state recurrence, chunk by chunk, and its output norm with the sigmoid gate
+//   activations                  xIELU and squared ReLU between the two products of a dense feed-forward
+//
+// Positions and angles, norms, gates, decays and the recurrent state are fp32 in both compute types.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "seq_engine.h"
+
+namespace kllm {
+namespace seq {
+namespace {
+
+constexpr unsigned kAll = 0xffffffffu;
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename AT> __device__ __forceinline__ AT from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kAll, v, o);
+  return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+__device__ __forceinline__ float sigmoidf(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float siluf(float z) { return z / (1.0f + expf(-z)); }
+
+// Rotary position: coordinate i < dims / 2 pairs with i + dims / 2; angle = pos * base^(-2 i / dims); coordinates past
+// `dims` pass unchanged.  v: the vector before rotation.
+__device__ __forceinline__ float rotated(const float* v, int i, int dims, float base, int pos) {
+  if (i >= dims) return v[i];
+  const int half = dims >> 1;
+  const int j = i < half ? i : i - half;
+  const float freq = exp2f(-2.0f * static_cast<float>(j) / static_cast<float>(dims) * log2f(base));
+  float sn, cs;
+  sincosf(static_cast<float>(pos) * freq, &sn, &cs);
+  return i < half ? v[i] * cs - v[i + half] * sn : v[i] * cs + v[i - half] * sn;
+}
+
+// ---- latent attention: down-projections -> normed query latent, cache row, gates -----------------------------------------
+template <typename AT>
+__global__ void latent_prepare_kernel(LatentShape a, const float* __restrict__ proj, const float* __restrict__ q_norm_w,
+                                      const float* __restrict__ kv_norm_w, float eps, const int32_t* __restrict__ tok_seq,
+                                      const int32_t* __restrict__ tok_pos, AT* __restrict__ cq, float* __restrict__ gates,
+                                      PagedKV kv) {
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const int stride = a.q_rank + a.kv_rank + a.rot_dim + a.heads;
+  const float* row = proj + static_cast<size_t>(t) * stride;
+  const int seq = tok_seq[t], pos = tok_pos[t];
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < a.q_rank; i += blockDim.x) ss += row[i] * row[i];
+  const float rq = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(a.q_rank) + eps);
+  for (int i = threadIdx.x; i < a.q_rank; i += blockDim.x)
+    cq[static_cast<size_t>(t) * a.q_rank + i] = from_f<AT>(row[i] * rq * q_norm_w[i]);
+  const float* c = row + a.q_rank;
+  ss = 0.f;
+  for (int i = threadIdx.x; i < a.kv_rank; i += blockDim.x) ss += c[i] * c[i];
+  const float rc = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(a.kv_rank) + eps);
+  const int page = kv.table[static_cast<size_t>(seq) * kv.table_stride + pos / kv.page];
+  AT* dst = static_cast<AT*>(kv.k) + (static_cast<size_t>(page) * kv.page + pos % kv.page) * kv.k_row;
+  for (int i = threadIdx.x; i < a.kv_rank; i += blockDim.x) dst[i] = from_f<AT>(c[i] * rc * kv_norm_w[i]);
+  const float* kr = c + a.kv_rank;
+  for (int i = threadIdx.x; i < a.rot_dim; i += blockDim.x)
+    dst[a.kv_rank + i] = from_f<AT>(rotated(kr, i, a.rope_dims, a.rope_base, pos));
+  const float* g = kr + a.rot_dim;
+  for (int h = threadIdx.x; h < a.heads; h += blockDim.x) gates[static_cast<size_t>(t) * a.heads + h] = sigmoidf(g[h]);
+}
+
+// ---- latent attention: queries into the latent space --------------------------------------------------------------------
+// One CTA: kAbsTokens tokens of one head.  qa[t, h, r] = sum_d q[t, h, d] * W_uk[h * dim + d, r]: thread r walks the
+// rows d of the head's block of W_uk (coalesced over r) with the tokens' queries in shared memory.
+constexpr int kAbsTokens = 16;
+template <typename AT>
+__global__ void latent_absorb_kernel(LatentShape a, const float* __restrict__ q, const AT* __restrict__ w_uk,
+                                     const int32_t* __restrict__ tok_pos, float* __restrict__ qa, int T) {
+  extern __shared__ float qs[];  // [kAbsTokens][dim + rot_dim]
+  const int h = blockIdx.y, t0 = blockIdx.x * kAbsTokens;
+  const int n = min(kAbsTokens, T - t0);
+  const int dq = a.dim + a.rot_dim, dl = a.kv_rank + a.rot_dim;
+  for (int i = threadIdx.x; i < n * dq; i += blockDim.x)
+    qs[i] = q[(static_cast<size_t>(t0 + i / dq) * a.heads + h) * dq + i % dq];
+  __syncthreads();
+  const AT* w = w_uk + static_cast<size_t>(h) * a.dim * a.kv_rank;
+  for (int r = threadIdx.x; r < a.kv_rank; r += blockDim.x) {
+    float acc[kAbsTokens];
+#pragma unroll
+    for (int j = 0; j < kAbsTokens; ++j) acc[j] = 0.f;
+    for (int d = 0; d < a.dim; ++d) {
+      const float wv = to_f(w[static_cast<size_t>(d) * a.kv_rank + r]);
+#pragma unroll
+      for (int j = 0; j < kAbsTokens; ++j) acc[j] = fmaf(qs[j * dq + d], wv, acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < kAbsTokens; ++j)
+      if (j < n) qa[(static_cast<size_t>(t0 + j) * a.heads + h) * dl + r] = acc[j];
+  }
+  for (int i = threadIdx.x; i < n * a.rot_dim; i += blockDim.x) {
+    const int j = i / a.rot_dim, c = i % a.rot_dim;
+    qa[(static_cast<size_t>(t0 + j) * a.heads + h) * dl + a.kv_rank + c] =
+        rotated(qs + j * dq + a.dim, c, a.rope_dims, a.rope_base, tok_pos[t0 + j]);
+  }
+}
+
+// ---- latent attention: weighted sums of latents -> per-head values ---------------------------------------------------------
+// One CTA: kAbsTokens tokens of one head; a warp per output row of W_uv's head block, dotted with every token's latent sum.
+template <typename AT>
+__global__ void latent_expand_kernel(LatentShape a, const float* __restrict__ ol, const AT* __restrict__ w_uv,
+                                     AT* __restrict__ out, int T) {
+  extern __shared__ float ls[];  // [kAbsTokens][kv_rank]
+  const int h = blockIdx.y, t0 = blockIdx.x * kAbsTokens;
+  const int n = min(kAbsTokens, T - t0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < kAbsTokens * a.kv_rank; i += blockDim.x) {
+    const int j = i / a.kv_rank;
+    ls[i] = j < n ? ol[(static_cast<size_t>(t0 + j) * a.heads + h) * a.kv_rank + i % a.kv_rank] : 0.f;
+  }
+  __syncthreads();
+  for (int f = warp; f < a.vdim; f += nw) {
+    const AT* w = w_uv + (static_cast<size_t>(h) * a.vdim + f) * a.kv_rank;
+    float acc[kAbsTokens];
+#pragma unroll
+    for (int j = 0; j < kAbsTokens; ++j) acc[j] = 0.f;
+    for (int r = lane; r < a.kv_rank; r += 32) {
+      const float wv = to_f(w[r]);
+#pragma unroll
+      for (int j = 0; j < kAbsTokens; ++j) acc[j] = fmaf(ls[j * a.kv_rank + r], wv, acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < kAbsTokens; ++j) {
+      const float v = warp_sum(acc[j]);
+      if (lane == 0 && j < n) out[(static_cast<size_t>(t0 + j) * a.heads + h) * a.vdim + f] = from_f<AT>(v);
+    }
+  }
+}
+
+// ---- linear attention ---------------------------------------------------------------------------------------------------------
+// Per head, with decay l:  S_t = l S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t.  Columns of S are independent, so one CTA takes
+// one entry, one head and kLinCols value columns, and walks the entry's tokens in chunks of kLinChunk.  For a chunk of n
+// tokens with the state S before it:
+//     o_i = l^(i+1) S^T q_i + sum_(j <= i) l^(i-j) (q_i . k_j) v_j
+//     S  <- l^n S + sum_j l^(n-1-j) k_j v_j^T
+// Only non-negative powers of l appear.  Everything is fp32; silu is applied to q, k, v as they are loaded.
+constexpr int kLinChunk = 32;
+constexpr int kLinCols = 32;
+constexpr int kLinThreads = 128;
+
+__global__ void __launch_bounds__(kLinThreads)
+linear_attention_kernel(int heads, int dim, int vdim, const float* __restrict__ decay, const float* __restrict__ proj,
+                        float* __restrict__ state, const int32_t* __restrict__ ent_first,
+                        const int32_t* __restrict__ ent_count, const int32_t* __restrict__ ent_seq,
+                        const int32_t* __restrict__ ent_pos0, float* __restrict__ o) {
+  extern __shared__ float sm[];
+  const int e = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * kLinCols;
+  const int count = ent_count[e], first = ent_first[e], seq = ent_seq[e];
+  const int cols = min(kLinCols, vdim - c0);
+  const int dp = dim + 1;
+  float* Qs = sm;                         // [chunk][dp]
+  float* Ks = Qs + kLinChunk * dp;        // [chunk][dp]
+  float* Vs = Ks + kLinChunk * dp;        // [chunk][kLinCols]
+  float* As = Vs + kLinChunk * kLinCols;  // [chunk][chunk + 1]
+  float* Ss = As + kLinChunk * (kLinChunk + 1);  // [dim][kLinCols]
+  float* pw = Ss + dim * kLinCols;        // [chunk + 1] powers of the decay
+  const int tid = threadIdx.x;
+  const float lam = decay[h];
+  const float llog = logf(lam);
+  if (tid <= kLinChunk) pw[tid] = tid == 0 ? 1.0f : expf(llog * static_cast<float>(tid));
+  float* sg = state + ((static_cast<size_t>(seq) * heads + h) * dim) * vdim;
+  const bool fresh = ent_pos0[e] == 0;
+  for (int i = tid; i < dim * kLinCols; i += kLinThreads) {
+    const int d = i / kLinCols, c = i % kLinCols;
+    Ss[i] = (!fresh && c < cols) ? sg[static_cast<size_t>(d) * vdim + c0 + c] : 0.f;
+  }
+  const int qn = heads * dim, vn = heads * vdim;
+  const int stride = 2 * qn + 2 * vn;
+  for (int base = 0; base < count; base += kLinChunk) {
+    const int n = min(kLinChunk, count - base);
+    __syncthreads();  // the previous chunk's tiles are no longer read; Ss / pw are written
+    for (int i = tid; i < n * dim; i += kLinThreads) {
+      const int j = i / dim, d = i % dim;
+      const float* row = proj + static_cast<size_t>(first + base + j) * stride;
+      Qs[j * dp + d] = siluf(row[h * dim + d]);
+      Ks[j * dp + d] = siluf(row[qn + h * dim + d]);
+    }
+    for (int i = tid; i < n * kLinCols; i += kLinThreads) {
+      const int j = i / kLinCols, c = i % kLinCols;
+      Vs[i] = c < cols ? siluf(proj[static_cast<size_t>(first + base + j) * stride + 2 * qn + h * vdim + c0 + c]) : 0.f;
+    }
+    __syncthreads();
+    for (int i = tid; i < n * n; i += kLinThreads) {  // decayed scores inside the chunk
+      const int r = i / n, j = i % n;
+      float acc = 0.f;
+      if (j <= r) {
+        for (int d = 0; d < dim; ++d) acc = fmaf(Qs[r * dp + d], Ks[j * dp + d], acc);
+        acc *= pw[r - j];
+      }
+      As[r * (kLinChunk + 1) + j] = acc;
+    }
+    __syncthreads();
+    for (int i = tid; i < n * kLinCols; i += kLinThreads) {  // outputs
+      const int r = i / kLinCols, c = i % kLinCols;
+      float carry = 0.f;
+      for (int d = 0; d < dim; ++d) carry = fmaf(Qs[r * dp + d], Ss[d * kLinCols + c], carry);
+      float acc = carry * pw[r + 1];
+      for (int j = 0; j <= r; ++j) acc = fmaf(As[r * (kLinChunk + 1) + j], Vs[j * kLinCols + c], acc);
+      if (c < cols) o[static_cast<size_t>(first + base + r) * vn + h * vdim + c0 + c] = acc;
+    }
+    __syncthreads();
+    for (int i = tid; i < dim * kLinCols; i += kLinThreads) {  // the state after the chunk
+      const int d = i / kLinCols, c = i % kLinCols;
+      float acc = Ss[i] * pw[n];
+      for (int j = 0; j < n; ++j) acc = fmaf(Ks[j * dp + d] * pw[n - 1 - j], Vs[j * kLinCols + c], acc);
+      Ss[i] = acc;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < dim * kLinCols; i += kLinThreads) {
+    const int d = i / kLinCols, c = i % kLinCols;
+    if (c < cols) sg[static_cast<size_t>(d) * vdim + c0 + c] = Ss[i];
+  }
+}
+
+template <typename AT>
+__global__ void linear_out_kernel(int qn, int vn, const float* __restrict__ o, const float* __restrict__ proj,
+                                  const float* __restrict__ norm_w, float eps, AT* __restrict__ out) {
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const float* row = o + static_cast<size_t>(t) * vn;
+  const float* g = proj + static_cast<size_t>(t) * (2 * qn + 2 * vn) + 2 * qn + vn;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < vn; i += blockDim.x) ss += row[i] * row[i];
+  const float rinv = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(vn) + eps);
+  for (int i = threadIdx.x; i < vn; i += blockDim.x)
+    out[static_cast<size_t>(t) * vn + i] = from_f<AT>(row[i] * rinv * norm_w[i] * sigmoidf(g[i]));
+}
+
+// ---- activations ---------------------------------------------------------------------------------------------------------------
+template <typename AT>
+__global__ void activation_kernel(int act, float a, float b, const float* __restrict__ z, AT* __restrict__ out, size_t n) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = z[i];
+  float r;
+  if (act == KLLM_SEQ_ACT_XIELU) r = v > 0.f ? a * v * v + 0.5f * v : b * (expm1f(v) - v) + 0.5f * v;
+  else r = v > 0.f ? v * v : 0.f;
+  out[i] = from_f<AT>(r);
+}
+
+__global__ void scale_kernel(float* __restrict__ v, float scale, size_t n) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) v[i] *= scale;
+}
+
+#define KLLM_SEQ_DISPATCH(dtype, CALL)                         \
+  do {                                                         \
+    if ((dtype) == KLLM_SEQ_F32) {                             \
+      using AT = float;                                        \
+      CALL;                                                    \
+    } else if ((dtype) == KLLM_SEQ_BF16) {                     \
+      using AT = __nv_bfloat16;                                \
+      CALL;                                                    \
+    } else {                                                   \
+      return KLLM_E_INVALID;                                   \
+    }                                                          \
+  } while (0)
+
+inline int done() {
+  count_launch();
+  return cuda_rc(cudaGetLastError());
+}
+}  // namespace
+
+int launch_latent_prepare(int dtype, const LatentShape& a, const float* proj, const float* q_norm_w, const float* kv_norm_w,
+                          float eps, const int32_t* tok_seq, const int32_t* tok_pos, void* cq, float* gates,
+                          const PagedKV& kv, int T, cudaStream_t s) {
+  KLLM_SEQ_DISPATCH(dtype, (latent_prepare_kernel<AT><<<T, 128, 0, s>>>(a, proj, q_norm_w, kv_norm_w, eps, tok_seq, tok_pos,
+                                                                       static_cast<AT*>(cq), gates, kv)));
+  return done();
+}
+
+int launch_latent_absorb(int dtype, const LatentShape& a, const float* q, const void* w_uk, const int32_t* tok_pos, float* qa,
+                         int T, cudaStream_t s) {
+  const size_t smem = static_cast<size_t>(kAbsTokens) * (a.dim + a.rot_dim) * sizeof(float);
+  if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
+  const dim3 grid((T + kAbsTokens - 1) / kAbsTokens, a.heads);
+  const int threads = a.kv_rank <= 64 ? 64 : (a.kv_rank <= 128 ? 128 : 256);
+  KLLM_SEQ_DISPATCH(dtype, (latent_absorb_kernel<AT><<<grid, threads, smem, s>>>(a, q, static_cast<const AT*>(w_uk), tok_pos,
+                                                                                qa, T)));
+  return done();
+}
+
+int launch_latent_expand(int dtype, const LatentShape& a, const float* ol, const void* w_uv, void* out, int T, cudaStream_t s) {
+  const size_t smem = static_cast<size_t>(kAbsTokens) * a.kv_rank * sizeof(float);
+  if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
+  const dim3 grid((T + kAbsTokens - 1) / kAbsTokens, a.heads);
+  KLLM_SEQ_DISPATCH(dtype, (latent_expand_kernel<AT><<<grid, 256, smem, s>>>(a, ol, static_cast<const AT*>(w_uv),
+                                                                            static_cast<AT*>(out), T)));
+  return done();
+}
+
+int launch_linear_attention(int heads, int dim, int vdim, const float* decay, const float* proj, float* state, int n_entries,
+                            const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
+                            const int32_t* ent_pos0, int max_count, float* o, cudaStream_t s) {
+  (void)max_count;
+  const size_t smem = (2 * static_cast<size_t>(kLinChunk) * (dim + 1) + kLinChunk * kLinCols + kLinChunk * (kLinChunk + 1) +
+                       static_cast<size_t>(dim) * kLinCols + kLinChunk + 1) * sizeof(float);
+  if (smem > 200 * 1024) return KLLM_E_UNSUPPORTED;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    const cudaError_t e = cudaFuncSetAttribute(linear_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(smem));
+    if (e != cudaSuccess) return cuda_rc(e);
+    configured = smem;
+  }
+  const dim3 grid((vdim + kLinCols - 1) / kLinCols, heads, n_entries);
+  linear_attention_kernel<<<grid, kLinThreads, smem, s>>>(heads, dim, vdim, decay, proj, state, ent_first, ent_count, ent_seq,
+                                                         ent_pos0, o);
+  return done();
+}
+
+int launch_linear_out(int dtype, int heads, int dim, int vdim, const float* o, const float* proj, const float* norm_w, float eps,
+                      void* out, int T, cudaStream_t s) {
+  KLLM_SEQ_DISPATCH(dtype, (linear_out_kernel<AT><<<T, 128, 0, s>>>(heads * dim, heads * vdim, o, proj, norm_w, eps,
+                                                                   static_cast<AT*>(out))));
+  return done();
+}
+
+int launch_activation(int dtype, int act, float a, float b, const float* z, void* out, size_t n, cudaStream_t s) {
+  if (act != KLLM_SEQ_ACT_XIELU && act != KLLM_SEQ_ACT_RELU2) return KLLM_E_UNSUPPORTED;
+  const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
+  KLLM_SEQ_DISPATCH(dtype, (activation_kernel<AT><<<blocks, 256, 0, s>>>(act, a, b, z, static_cast<AT*>(out), n)));
+  return done();
+}
+
+int launch_scale(float* v, float scale, size_t n, cudaStream_t s) {
+  scale_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(v, scale, n);
+  return done();
+}
+
+}  // namespace seq
+}  // namespace kllm

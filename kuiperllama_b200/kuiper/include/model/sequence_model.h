@@ -79,6 +79,12 @@ class SequenceModel : public base::NoCopyable {
   // one tensor as fp32 on the device, checked against `numel`
   base::Status upload_f32(const StTensor* t, int64_t numel, const float** device);
   const StTensor* need(const SafetensorsFile& f, const std::string& name, base::Status* status) const;
+  // host values as fp32 on the device
+  base::Status upload_values(const std::vector<float>& values, const float** device);
+  // a tensor that holds ONE number, repeated `numel` times on the device (a norm whose weight is a single number)
+  base::Status upload_broadcast(const StTensor* t, int64_t numel, const float** device);
+  // the values of a small tensor on the host, checked against `numel`
+  base::Status read_values(const StTensor* t, int64_t numel, std::vector<float>* out) const;
 
   ComputeType compute_ = ComputeType::kBFloat16;
   int32_t vocab_ = 0, width_ = 0;
@@ -88,7 +94,10 @@ class SequenceModel : public base::NoCopyable {
   const float* run_vectors_ = nullptr;
   const void* embed_ = nullptr;
   const void* head_ = nullptr;
-  kllm_seq_norm final_norm_{nullptr, nullptr};
+  kllm_seq_norm final_norm_{nullptr, nullptr, KLLM_SEQ_NORM_LAYER};
+  kllm_seq_norm embed_norm_{nullptr, nullptr, KLLM_SEQ_NORM_LAYER};  // w == nullptr: the embedding rows are used as they are
+  std::vector<int32_t> run_embed_;  // per layer run (or empty): add the embedding output before the run
+  float logit_scale_ = 1.0f;
 
  private:
   SequenceOptions options_;

@@ -76,6 +76,28 @@ base::Status SequenceModel::upload_f32(const StTensor* t, int64_t numel, const f
   return base::error::Success();
 }
 
+base::Status SequenceModel::upload_values(const std::vector<float>& values, const float** device) {
+  auto buf = device_alloc(values.size() * 4);
+  if (!buf) return base::error::InternalError("device allocation failed");
+  if (!values.empty() && cudaMemcpy(buf->ptr(), values.data(), values.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess)
+    return base::error::InternalError("weight upload failed");
+  *device = static_cast<const float*>(buf->ptr());
+  return base::error::Success();
+}
+
+base::Status SequenceModel::read_values(const StTensor* t, int64_t numel, std::vector<float>* out) const {
+  if (t == nullptr) return base::error::ModelParseError("a tensor is missing");
+  if (t->numel() != numel) return base::error::ModelParseError("a tensor has an unexpected size");
+  out->assign(static_cast<size_t>(numel), 0.f);
+  return tensor_to_f32(*t, out->data());
+}
+
+base::Status SequenceModel::upload_broadcast(const StTensor* t, int64_t numel, const float** device) {
+  std::vector<float> one;
+  if (base::Status st = read_values(t, 1, &one); !st) return st;
+  return upload_values(std::vector<float>(static_cast<size_t>(numel), one[0]), device);
+}
+
 const StTensor* SequenceModel::need(const SafetensorsFile& f, const std::string& name, base::Status* status) const {
   const StTensor* t = f.find(name);
   if (t == nullptr && *status) *status = base::error::ModelParseError("tensor '" + name + "' is missing");
@@ -110,6 +132,8 @@ base::Status SequenceModel::init(const std::string& dir, const SequenceOptions& 
   d.n_runs = static_cast<int32_t>(run_layer_.size()), d.run_layer = run_layer_.data(), d.run_add = run_add_.data();
   d.run_vectors = run_vectors_, d.embed = embed_, d.final_norm = final_norm_, d.head = head_;
   d.max_tokens = options.max_tokens, d.max_seqs = options.max_seqs, d.page_tokens = options.page_tokens;
+  d.embed_norm = embed_norm_, d.logit_scale = logit_scale_;
+  d.run_embed = run_embed_.size() == run_layer_.size() ? run_embed_.data() : nullptr;
   return engine_status(kllm_seq_create(&d, nullptr, &engine_), "kllm_seq_create");
 }
 

@@ -17,7 +17,7 @@ PHASES = ["norm", "in_proj", "qk_prepare", "attention", "out_proj", "router", "e
 
 
 class Norm(ctypes.Structure):
-    _fields_ = [("w", c_void_p), ("b", c_void_p)]
+    _fields_ = [("w", c_void_p), ("b", c_void_p), ("kind", c_int32)]
 
 
 class Attention(ctypes.Structure):
@@ -29,19 +29,40 @@ class Attention(ctypes.Structure):
 class Moe(ctypes.Structure):
     _fields_ = [("experts", c_int32), ("top", c_int32), ("ff", c_int32), ("router_scale", c_float),
                 ("w_router", c_void_p), ("gate_up", c_void_p), ("down", c_void_p), ("shared_ff", c_int32),
-                ("shared_gate_up", c_void_p), ("shared_down", c_void_p), ("w_shared_gate", c_void_p)]
+                ("shared_gate_up", c_void_p), ("shared_down", c_void_p), ("w_shared_gate", c_void_p),
+                ("router_kind", c_int32), ("correction", c_void_p), ("groups", c_int32), ("groups_keep", c_int32),
+                ("act", c_int32)]
+
+
+class Latent(ctypes.Structure):
+    _fields_ = [("heads", c_int32), ("dim", c_int32), ("rot_dim", c_int32), ("vdim", c_int32), ("q_rank", c_int32),
+                ("kv_rank", c_int32), ("scale", c_float), ("window", c_int32), ("rope_dims", c_int32),
+                ("rope_base", c_float), ("w_in", c_void_p), ("q_norm_w", c_void_p), ("kv_norm_w", c_void_p),
+                ("w_uq", c_void_p), ("w_uk", c_void_p), ("w_uv", c_void_p), ("sink", c_void_p), ("w_out", c_void_p)]
+
+
+class Linear(ctypes.Structure):
+    _fields_ = [("heads", c_int32), ("dim", c_int32), ("vdim", c_int32), ("decay", c_void_p), ("w_in", c_void_p),
+                ("out_norm_w", c_void_p), ("w_out", c_void_p)]
+
+
+class Dense(ctypes.Structure):
+    _fields_ = [("ff", c_int32), ("act", c_int32), ("act_a", c_float), ("act_b", c_float), ("up", c_void_p),
+                ("down", c_void_p)]
 
 
 class Layer(ctypes.Structure):
     _fields_ = [("mixer_kind", c_int32), ("ff_kind", c_int32), ("pre_mixer", Norm), ("post_mixer", Norm),
-                ("pre_ff", Norm), ("post_ff", Norm), ("attn", Attention), ("moe", Moe)]
+                ("pre_ff", Norm), ("post_ff", Norm), ("attn", Attention), ("moe", Moe), ("shift", c_void_p),
+                ("latent", Latent), ("linear", Linear), ("dense", Dense)]
 
 
 class Desc(ctypes.Structure):
     _fields_ = [("dtype", c_int32), ("width", c_int32), ("vocab", c_int32), ("norm_eps", c_float),
                 ("n_layers", c_int32), ("layers", POINTER(Layer)), ("n_runs", c_int32), ("run_layer", POINTER(c_int32)),
                 ("run_add", POINTER(c_int32)), ("run_vectors", c_void_p), ("embed", c_void_p), ("final_norm", Norm),
-                ("head", c_void_p), ("max_tokens", c_int32), ("max_seqs", c_int32), ("page_tokens", c_int32)]
+                ("head", c_void_p), ("max_tokens", c_int32), ("max_seqs", c_int32), ("page_tokens", c_int32),
+                ("embed_norm", Norm), ("run_embed", POINTER(c_int32)), ("logit_scale", c_float)]
 
 
 class SeqError(RuntimeError):
