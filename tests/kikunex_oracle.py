@@ -78,7 +78,7 @@ def latent_attention(h, w, p, m, eps):
     k_plain = (c @ w[p + "uk"].T).reshape(T, H, dn)
     v = (c @ w[p + "uv"].T).reshape(T, H, dv)
     gate = sigmoid(h @ w[p + "g"].T)                                            # [T, H]
-    window = m["mask"]["size"]
+    window = m["mask"]["size"] if m.get("mask") else T
     out = np.zeros((T, H, dv))
     for i in range(T):
         lo = max(0, i - window + 1)
@@ -183,3 +183,128 @@ def forward(config, weights, tokens):
         trace.append(x.copy())
     logits = scalar_norm(x, w["final.norm"], eps) @ w["head"].T * config["logit_scale"]
     return logits, np.stack(trace)
+
+
+def greedy(config, weights, prompt, n_new):
+    """Greedy continuation by recomputing the whole sequence (lowest index on ties)."""
+    seq, out = list(prompt), []
+    for _ in range(n_new):
+        logits, _ = forward(config, weights, seq)
+        out.append(int(np.argmax(logits[-1])))
+        seq.append(out[-1])
+    return out
+
+
+# ---- small random models for the tests ------------------------------------------------------------------------------------
+def latent_mixer(heads=4, dim=12, rot_dim=8, vdim=10, kv_rank=24, q_rank=20, window=16, base=10000.0, scale=None,
+                 rot_dims=None):
+    return {"type": "latent_attention",
+            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
+                      "mask": {"size": window}, "rot": {"base": base, "dims": rot_dim if rot_dims is None else rot_dims},
+                      "scale": (dim + rot_dim) ** -0.5 if scale is None else scale}}
+
+
+def lightning_mixer(heads=3, dim=8, vdim=12, decay=None):
+    decay = [math.exp(-1.0 / (2.0 + 7.0 * h)) for h in range(heads)] if decay is None else list(decay)
+    return {"type": "lightning", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay}}
+
+
+def dense_mlp(ff=40):
+    return {"kind": "dense", "ff": ff}
+
+
+def moe_mlp(experts=6, top=2, ff=16, groups=(3, 2), scale=1.5):
+    r = {"experts": experts, "top": top, "scale": scale}
+    if groups:
+        r["groups"] = {"count": groups[0], "keep": groups[1]}
+    return {"kind": "moe", "expert": {"ff": ff}, "router": r}
+
+
+def make_config(width=48, vocab=61, layers=(), loop=None, eps=1e-5, logit_scale=0.7):
+    """layers: [(mixer dict, mlp dict or None)]."""
+    cfg = {"architecture": "Kikunex", "vocab": vocab, "width": width, "norm": {"eps": eps}, "logit_scale": logit_scale,
+           "layers": [dict(m, mlp=f) for m, f in layers]}
+    if loop:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def bf16_round(a):
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    u = ((u + 0x7fff + ((u >> 16) & 1)) >> 16) << 16
+    return u.astype(np.uint32).view(np.float32).astype(np.float64)
+
+
+def make_weights(cfg, seed=0, sharp=1.0):
+    """Random bf16-representable weights.  `sharp` multiplies the query latent's norm weight: > 1 makes the softmax
+    peaky, so that single keys (those at a window's edge too) carry the output."""
+    rng = np.random.default_rng(seed)
+    W, V = cfg["width"], cfg["vocab"]
+
+    def rnd(*shape, std=1.0, mean=0.0):
+        return bf16_round(mean + std * rng.standard_normal(shape))
+    w = {"embed": rnd(V, W), "embed.norm": rnd(mean=1.0, std=0.1), "head": rnd(V, W, std=W ** -0.5),
+         "final.norm": rnd(mean=1.0, std=0.1)}
+    if cfg.get("loop"):
+        w["loop.step"] = rnd(cfg["loop"]["times"], W, std=0.5)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        w[p + "norm1"] = rnd(mean=1.0, std=0.1)
+        w[p + "shift"] = bf16_round(rng.uniform(0.0, 1.0, W))
+        H = m["heads"]
+        if L["type"] == "latent_attention":
+            w[p + "mix.dq"] = rnd(m["q_rank"], W, std=W ** -0.5)
+            w[p + "mix.dq.norm"] = rnd(m["q_rank"], mean=1.0, std=0.1) * sharp
+            w[p + "mix.dq.norm"] = bf16_round(w[p + "mix.dq.norm"])
+            w[p + "mix.uq"] = rnd(H * (m["dim"] + m["rot_dim"]), m["q_rank"], std=m["q_rank"] ** -0.5)
+            w[p + "mix.dkv"] = rnd(m["kv_rank"] + m["rot_dim"], W, std=W ** -0.5)
+            w[p + "mix.dkv.norm"] = rnd(m["kv_rank"], mean=1.0, std=0.1)
+            w[p + "mix.uk"] = rnd(H * m["dim"], m["kv_rank"], std=m["kv_rank"] ** -0.5)
+            w[p + "mix.uv"] = rnd(H * m["vdim"], m["kv_rank"], std=m["kv_rank"] ** -0.5)
+            w[p + "mix.sink"] = rnd(H)
+            w[p + "mix.g"] = rnd(H, W, std=W ** -0.5)
+            w[p + "mix.o"] = rnd(W, H * m["vdim"], std=(H * m["vdim"]) ** -0.5)
+        else:
+            for n, rows in (("q", H * m["dim"]), ("k", H * m["dim"]), ("v", H * m["vdim"]), ("g", H * m["vdim"])):
+                w[p + "mix." + n] = rnd(rows, W, std=W ** -0.5)
+            w[p + "mix.norm"] = rnd(H * m["vdim"], mean=1.0, std=0.1)
+            w[p + "mix.o"] = rnd(W, H * m["vdim"], std=(H * m["vdim"]) ** -0.5)
+        f = L.get("mlp")
+        if not f:
+            continue
+        w[p + "norm2"] = rnd(mean=1.0, std=0.1)
+        if f["kind"] == "dense":
+            w[p + "mlp.up"] = rnd(f["ff"], W, std=W ** -0.5)
+            w[p + "mlp.down"] = rnd(W, f["ff"], std=f["ff"] ** -0.5)
+            w[p + "mlp.act"] = rnd(2, std=0.7)
+        else:
+            E, ff = f["router"]["experts"], f["expert"]["ff"]
+            for e in range(E):
+                w[f"{p}mlp.e{e}.up"] = rnd(ff, W, std=W ** -0.5)
+                w[f"{p}mlp.e{e}.down"] = rnd(W, ff, std=ff ** -0.5)
+            w[p + "mlp.router"] = rnd(E, W, std=2.0 * W ** -0.5)
+            w[p + "mlp.correction"] = rnd(E, std=0.3)
+    return w
+
+
+def write_model(folder, cfg, weights):
+    """config.json and model.safetensors (bfloat16) in `folder`."""
+    import json
+    import struct
+    from pathlib import Path
+    folder = Path(folder)
+    folder.mkdir(parents=True, exist_ok=True)
+    (folder / "config.json").write_text(json.dumps(cfg))
+    header, blobs, at = {}, [], 0
+    for name, a in weights.items():
+        u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+        assert not (u & 0xffff).any(), f"{name} is not bf16-representable"
+        raw = (u >> 16).astype("<u2").tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(np.shape(a)), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    head = json.dumps(header).encode()
+    head += b" " * (-len(head) % 8)
+    with open(folder / "model.safetensors", "wb") as f:
+        f.write(struct.pack("<Q", len(head)) + head + b"".join(blobs))
+    return folder
