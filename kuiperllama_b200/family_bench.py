@@ -18,7 +18,7 @@ import statistics
 import time
 from pathlib import Path
 
-from .sequence import BF16, F32, FobolornShape, SeqEngine, load_seq_library
+from .sequence import BF16, F32, FobolornShape, KikunexShape, SeqEngine, load_seq_library
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -29,6 +29,51 @@ SIZES = {
     "m": FobolornShape("fobolorn-m", 2048, 32000, 4, (1, 3, 2), 16, 4, 128, 128, 32, 4, 768, 2048),
     "debug": FobolornShape("fobolorn-debug", 256, 4096, 3, (1, 3, 2), 4, 2, 64, 64, 8, 2, 128, 256),
 }
+
+
+_KP = (("lightning", "dense"), ("latent", "moe"), ("lightning", "moe"), ("latent", "moe"))
+KIKUNEX_SIZES = {
+    # the sizes of SIZES, layer for layer: same width, head counts, experts and layer runs; latent attention with a
+    # key/value rank of two head sizes and a window of a quarter of the prompt, linear attention with square states
+    "s": KikunexShape("kikunex-s", 1024, 32000, _KP, (1, 3, 2), 16, 64, 32, 64, 384, 128, 512, 16, 64, 64, 2048, 16, 2, 512),
+    "m": KikunexShape("kikunex-m", 2048, 32000, _KP, (1, 3, 2), 16, 128, 64, 128, 768, 256, 512, 16, 128, 128, 4096, 32, 4, 768),
+    "debug": KikunexShape("kikunex-debug", 256, 4096, _KP[:3], (1, 3, 2), 4, 32, 16, 32, 96, 64, 96, 4, 32, 32, 512, 8, 2, 128),
+}
+
+
+def kikunex_costs(shape, prompt_len):
+    """FLOPs of a prompt step and bytes of a decode step, by phase class of the engine's profile."""
+    W = shape.width
+    runs = [shape.pattern[i] for i, _, _ in shape.run_order()]
+    n_lat = sum(1 for m, _ in runs if m == "latent")
+    n_lin = len(runs) - n_lat
+    win = min(shape.window, prompt_len)
+    pairs = prompt_len * win - win * (win - 1) / 2  # (query, key) pairs inside the window
+    H, r, dr = shape.heads, shape.kv_rank, shape.rot_dim
+    # latent attention as the engine computes it: scores and sums over the latent; absorb and expand per token
+    attn_lat = 2 * pairs * H * (2 * r + dr) + 2 * prompt_len * H * r * (shape.dim + shape.vdim)
+    chunk = 32
+    attn_lin = 2 * prompt_len * shape.lin_heads * (chunk / 2 * (shape.lin_dim + shape.lin_vdim) +
+                                                    2 * shape.lin_dim * shape.lin_vdim)
+    flops = {"in_proj": 2 * prompt_len * W * (n_lat * shape.n_in("latent") + n_lin * shape.n_in("lightning")),
+             "qk_prepare": 2 * prompt_len * n_lat * H * (shape.dim + dr) * shape.q_rank,
+             "attention": n_lat * attn_lat + n_lin * attn_lin,
+             "out_proj": 2 * prompt_len * W * (n_lat * H * shape.vdim + n_lin * shape.lin_heads * shape.lin_vdim),
+             "experts": 2 * prompt_len * sum(shape.ff_weight_elems(f, shape.top) - (shape.experts * W if f == "moe" else 0)
+                                             for _, f in runs),
+             "head": 2 * shape.vocab * W}
+    return flops
+
+
+def fobolorn_costs(shape, prompt_len):
+    W = shape.width
+    R = shape.runs
+    return {"in_proj": 2 * prompt_len * W * shape.n_in() * R,
+            "attention": 2 * prompt_len * prompt_len / 2 * (shape.dim + shape.vdim) * shape.heads * R,
+            "out_proj": 2 * prompt_len * W * shape.heads * shape.vdim * R,
+            "experts": 2 * prompt_len * shape.top * 3 * shape.ff * W * R,
+            "shared": 2 * prompt_len * 3 * shape.shared_ff * W * R,
+            "head": 2 * shape.vocab * W}
 
 
 def peaks():
@@ -90,11 +135,14 @@ def bench_engine(torch, shape, dtype, prompt_len, ctx, batches, steps, warm, flu
     launches = eng.launches()
     eng.close_seq(s)
     sec = statistics.median(times)
-    flops = shape.flops_per_token() * prompt_len + \
-        2 * prompt_len * prompt_len / 2 * (shape.dim + shape.vdim) * shape.heads * shape.runs
+    kiku = isinstance(shape, KikunexShape)
+    phase_flops = kikunex_costs(shape, prompt_len) if kiku else fobolorn_costs(shape, prompt_len)
+    flops = sum(phase_flops.values())
     out["prefill"] = {"tokens": prompt_len, "tok_s": prompt_len / sec, "ms": sec * 1e3, "launches": launches,
                       "tflops": flops / sec / 1e12, "frac_of_bf16_peak": flops / sec / 1e12 / tf if dtype == BF16 else None,
-                      "phase_ms": ph}
+                      "phase_ms": ph,
+                      "phase_tflops": {k: (v / (ph[k] * 1e-3) / 1e12 if ph.get(k, 0) > 0 else None)
+                                       for k, v in phase_flops.items()}}
     # ---- decode: B sequences at context ctx, one token each per step ---------------------------------------------
     out["decode"] = {}
     for B in batches:
@@ -118,6 +166,23 @@ def bench_engine(torch, shape, dtype, prompt_len, ctx, batches, steps, warm, flu
         # bytes a step must read: the active weights (distinct experts per token, an upper bound when tokens share
         # experts) and the cached keys / values
         W = shape.width
+        if kiku:
+            runs = [shape.pattern[i] for i, _, _ in shape.run_order()]
+            state = shape.state_bytes_per_step(B, ctx, es)
+            bytes_step = shape.weight_elems_per_step(B) * es + state
+            phase_bytes = {"in_proj": sum(shape.n_in(m) for m, _ in runs) * W * es,
+                           "out_proj": sum(shape.heads * shape.vdim if m == "latent" else shape.lin_heads * shape.lin_vdim
+                                           for m, _ in runs) * W * es,
+                           "experts": sum(shape.ff_weight_elems(f, B * shape.top) - (shape.experts * W if f == "moe" else 0)
+                                          for _, f in runs) * es,
+                           "attention": state + sum(shape.heads * shape.vdim * shape.kv_rank for m, _ in runs if m == "latent") * es,
+                           "head": shape.vocab * W * es}
+            out["decode"][str(B)] = {
+                "batch": B, "context": ctx, "tok_s": B / sec, "ms_per_step": sec * 1e3, "launches": launches,
+                "bytes_per_step": bytes_step, "frac_of_hbm_peak": bytes_step / sec / 1e9 / hbm, "phase_ms": ph,
+                "phase_frac_of_hbm_peak": {k: (v / (ph[k] * 1e-3) / 1e9 / hbm if ph[k] > 0 else None)
+                                           for k, v in phase_bytes.items()}}
+            continue
         per_run_shared = (shape.n_in() * W + W * shape.heads * shape.vdim + 3 * shape.shared_ff * W) * es + shape.experts * W * 4
         per_run_experts = min(B * shape.top, shape.experts) * 3 * shape.ff * W * es
         kv = B * ctx * shape.kv_heads * (shape.dim + shape.vdim) * es
@@ -238,6 +303,8 @@ def run(args, emit):
     flush = Flusher(torch)
     sizes = [s for s in (args.family_sizes.split(",") if args.family_sizes else ["s", "m"])]
     steps, warm = max(3, min(args.steps, 16)), max(3, min(args.warmup, 8))
+    if args.family == "kikunex":
+        return run_kikunex(args, emit, torch, sizes, steps, warm, flush, hbm, tf, src)
     line = {"family": "fobolorn", "metric": "prefill_and_decode_tokens_per_s", "n_gpus": 1, "steps": steps, "warmup": warm,
             "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
             "config": {"l2": "a 256 MiB buffer is written between timed steps", "timing": "wall clock around the blocking "
@@ -251,5 +318,25 @@ def run(args, emit):
             entry["fobolorn"].append(bench_engine(torch, shape, dtype, prompt, ctx, [1, 8], steps, warm, flush, hbm, tf))
         entry["closest"] = bench_llama(torch, shape, ctx, max(steps, 32), warm, hbm, tf)
         entry["kernels"] = bench_kernels(torch, shape, flush, hbm, tf)
+        line["sizes"][name] = entry
+    emit(line)
+
+
+def run_kikunex(args, emit, torch, sizes, steps, warm, flush, hbm, tf, src):
+    """Kikunex beside its closest existing model, Fobolorn (the same engine), at equal width, heads, experts and layer
+    runs: whole steps end to end, and the engine's phase classes side by side."""
+    line = {"family": "kikunex", "metric": "prefill_and_decode_tokens_per_s", "n_gpus": 1, "steps": steps, "warmup": warm,
+            "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+            "config": {"l2": "a 256 MiB buffer is written between timed steps", "timing": "wall clock around the blocking "
+                       "step call (token ids from host memory, greedy ids back to host memory); phases by CUDA events"},
+            "sizes": {}}
+    for name in sizes:
+        shape, close = KIKUNEX_SIZES[name], SIZES[name]
+        ctx, prompt = (256, 512) if name == "debug" else (1024, 2048)
+        entry = {"shape": {k: v for k, v in shape.__dict__.items()} | {"runs": shape.runs}, "kikunex": [], "closest": []}
+        for dtype in (BF16, F32):
+            entry["kikunex"].append(bench_engine(torch, shape, dtype, prompt, ctx, [1, 8], steps, warm, flush, hbm, tf))
+            entry["closest"].append(bench_engine(torch, close, dtype, prompt, ctx, [1, 8], steps, warm, flush, hbm, tf))
+        entry["closest_model"] = close.name
         line["sizes"][name] = entry
     emit(line)

@@ -2,7 +2,7 @@
 device memory, the engine and every kernel are the product library's.  Like the rest of this package it has no
 fallback: without libkllm_seq.so (or libkllm_b200.so, which carries the same symbols) it raises.
 
-`FobolornShape` + `synth_fobolorn()` build a random-weight model of the Fobolorn family directly in device memory
+`FobolornShape` / `KikunexShape` + `SeqEngine` build a random-weight model of a family directly in device memory
 (no model folder), for measurements at sizes that resemble a real model's layers.
 """
 from __future__ import annotations
@@ -136,14 +136,104 @@ class FobolornShape:
         return 2 * self.active_weight_elems_per_token()
 
 
-class SeqEngine:
-    """A random-weight Fobolorn model in device memory behind the engine's C-ABI."""
+@dataclass
+class KikunexShape:
+    """A Kikunex model: `pattern` lists the layers ("lightning" | "latent", "dense" | "moe" | None)."""
+    name: str
+    width: int
+    vocab: int
+    pattern: tuple
+    loop: tuple          # (start, stop, times)
+    heads: int           # latent attention
+    dim: int
+    rot_dim: int
+    vdim: int
+    q_rank: int
+    kv_rank: int
+    window: int
+    lin_heads: int       # linear attention
+    lin_dim: int
+    lin_vdim: int
+    dense_ff: int
+    experts: int
+    top: int
+    ff: int
+    groups: tuple = (4, 2)
+    eps: float = 1e-5
 
-    def __init__(self, shape: FobolornShape, dtype=BF16, max_tokens=4096, max_seqs=16, page=0, seed=1):
+    @property
+    def layers(self):
+        return len(self.pattern)
+
+    def run_order(self):
+        s, e, t = self.loop
+        order = [(i, -1, 0) for i in range(s)]
+        for p in range(t):
+            order += [(i, p if i == s else -1, 1 if i == s and p > 0 else 0) for i in range(s, e)]
+        return order + [(i, -1, 0) for i in range(e, self.layers)]
+
+    @property
+    def runs(self):
+        return len(self.run_order())
+
+    def n_in(self, kind):
+        if kind == "latent":
+            return self.q_rank + self.kv_rank + self.rot_dim + self.heads
+        return 2 * self.lin_heads * (self.lin_dim + self.lin_vdim)
+
+    def mixer_weight_elems(self, kind):
+        W = self.width
+        if kind == "latent":
+            return self.n_in(kind) * W + self.heads * (self.dim + self.rot_dim) * self.q_rank + \
+                self.heads * (self.dim + self.vdim) * self.kv_rank + W * self.heads * self.vdim
+        return self.n_in(kind) * W + W * self.lin_heads * self.lin_vdim
+
+    def ff_weight_elems(self, kind, pairs):
+        W = self.width
+        if kind == "dense":
+            return 2 * self.dense_ff * W
+        if kind == "moe":
+            return self.experts * W + min(pairs, self.experts) * 2 * self.ff * W
+        return 0
+
+    def weight_elems_per_step(self, batch):
+        """Matrix elements a decode step of `batch` sequences reads (distinct experts: an upper bound)."""
+        total = self.vocab * self.width
+        for i, _, _ in self.run_order():
+            m, f = self.pattern[i]
+            total += self.mixer_weight_elems(m) + self.ff_weight_elems(f, batch * self.top)
+        return total
+
+    def flops_per_token(self):
+        total = self.vocab * self.width
+        for i, _, _ in self.run_order():
+            m, f = self.pattern[i]
+            total += self.mixer_weight_elems(m) + self.ff_weight_elems(f, self.top) - (self.experts * 0 if f != "moe" else 0)
+        return 2 * total
+
+    def state_bytes_per_step(self, batch, ctx, es):
+        """Cache and state a decode step touches: the window's latents, the linear-attention state (read and written)."""
+        total = 0
+        for i, _, _ in self.run_order():
+            m, _ = self.pattern[i]
+            if m == "latent":
+                total += batch * min(ctx, self.window) * (self.kv_rank + self.rot_dim) * es
+            else:
+                total += batch * 2 * self.lin_heads * self.lin_dim * self.lin_vdim * 4
+        return total
+
+
+class SeqEngine:
+    """A random-weight model (Fobolorn or Kikunex, by the shape's class) in device memory behind the engine's C-ABI."""
+
+    def __init__(self, shape, dtype=BF16, max_tokens=4096, max_seqs=16, page=0, seed=1):
         import torch
         self.torch = torch
         self.lib = load_seq_library()
         self.shape, self.dtype = shape, dtype
+        if isinstance(shape, KikunexShape):
+            self._init_kikunex(shape, dtype, max_tokens, max_seqs, page, seed)
+            return
         td = torch.bfloat16 if dtype == BF16 else torch.float32
         g = torch.Generator(device="cuda").manual_seed(seed)
         keep = self._keep = []
@@ -196,6 +286,91 @@ class SeqEngine:
         self._desc = (d, layers, run_layer, run_add)
         self.handle = c_void_p()
         torch.cuda.synchronize()  # the engine runs on a stream of its own: the weights must be complete first
+        _check(self.lib, self.lib.kllm_seq_create(ctypes.byref(d), None, ctypes.byref(self.handle)), "kllm_seq_create")
+
+    def _init_kikunex(self, shape, dtype, max_tokens, max_seqs, page, seed):
+        torch = self.torch
+        td = torch.bfloat16 if dtype == BF16 else torch.float32
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        keep = self._keep = []
+        W = shape.width
+
+        def rnd(*dims, std, t=td, mean=0.0):
+            x = (torch.randn(*dims, device="cuda", generator=g) * std + mean).to(t).contiguous()
+            keep.append(x)
+            return x
+
+        def f32(*dims, std, mean=0.0):
+            return rnd(*dims, std=std, t=torch.float32, mean=mean)
+
+        def norm():
+            w = torch.full((W,), 1.0 + 0.05 * float(torch.randn((), generator=torch.Generator().manual_seed(len(keep)))),
+                           device="cuda")
+            keep.append(w)
+            return Norm(w.data_ptr(), None, 1)
+
+        layers = (Layer * shape.layers)()
+        for L, (mix, ff) in zip(layers, shape.pattern):
+            L.pre_mixer = norm()
+            L.shift = f32(W, std=0.2, mean=0.5).data_ptr()
+            if mix == "latent":
+                L.mixer_kind = 2
+                a = L.latent
+                a.heads, a.dim, a.rot_dim, a.vdim = shape.heads, shape.dim, shape.rot_dim, shape.vdim
+                a.q_rank, a.kv_rank, a.window = shape.q_rank, shape.kv_rank, shape.window
+                a.scale, a.rope_dims, a.rope_base = (shape.dim + shape.rot_dim) ** -0.5, shape.rot_dim, 10000.0
+                a.w_in = rnd(shape.n_in("latent"), W, std=W ** -0.5).data_ptr()
+                a.q_norm_w = f32(shape.q_rank, std=0.05, mean=1.0).data_ptr()
+                a.kv_norm_w = f32(shape.kv_rank, std=0.05, mean=1.0).data_ptr()
+                a.w_uq = rnd(shape.heads * (shape.dim + shape.rot_dim), shape.q_rank, std=shape.q_rank ** -0.5).data_ptr()
+                a.w_uk = rnd(shape.heads * shape.dim, shape.kv_rank, std=shape.kv_rank ** -0.5).data_ptr()
+                a.w_uv = rnd(shape.heads * shape.vdim, shape.kv_rank, std=shape.kv_rank ** -0.5).data_ptr()
+                a.sink = f32(shape.heads, std=1.0).data_ptr()
+                a.w_out = rnd(W, shape.heads * shape.vdim, std=(shape.heads * shape.vdim) ** -0.5).data_ptr()
+            else:
+                L.mixer_kind = 3
+                a = L.linear
+                a.heads, a.dim, a.vdim = shape.lin_heads, shape.lin_dim, shape.lin_vdim
+                decay = torch.tensor([math.exp(-1.0 / (4.0 * (h + 1))) for h in range(shape.lin_heads)], device="cuda")
+                keep.append(decay)
+                a.decay = decay.data_ptr()
+                a.w_in = rnd(shape.n_in("lightning"), W, std=W ** -0.5).data_ptr()
+                a.out_norm_w = f32(shape.lin_heads * shape.lin_vdim, std=0.05, mean=1.0).data_ptr()
+                a.w_out = rnd(W, shape.lin_heads * shape.lin_vdim, std=(shape.lin_heads * shape.lin_vdim) ** -0.5).data_ptr()
+            L.ff_kind = {None: 0, "moe": 1, "dense": 2}[ff]
+            if ff is not None:
+                L.pre_ff = norm()
+            if ff == "dense":
+                d = L.dense
+                d.ff, d.act, d.act_a, d.act_b = shape.dense_ff, 2, 0.6, 1.1
+                d.up = rnd(shape.dense_ff, W, std=W ** -0.5).data_ptr()
+                d.down = rnd(W, shape.dense_ff, std=0.3 * shape.dense_ff ** -0.5).data_ptr()
+            elif ff == "moe":
+                m = L.moe
+                m.experts, m.top, m.ff, m.router_scale = shape.experts, shape.top, shape.ff, 1.5
+                m.router_kind, m.act = 1, 1
+                m.groups, m.groups_keep = shape.groups
+                m.w_router = f32(shape.experts, W, std=W ** -0.5).data_ptr()
+                m.correction = f32(shape.experts, std=0.1).data_ptr()
+                m.gate_up = rnd(shape.experts, shape.ff, W, std=W ** -0.5).data_ptr()
+                m.down = rnd(shape.experts, W, shape.ff, std=0.3 * shape.ff ** -0.5).data_ptr()
+        order = shape.run_order()
+        run_layer = (c_int32 * len(order))(*[i for i, _, _ in order])
+        run_add = (c_int32 * len(order))(*[p for _, p, _ in order])
+        run_embed = (c_int32 * len(order))(*[x for _, _, x in order])
+        d = Desc()
+        d.dtype, d.width, d.vocab, d.norm_eps = dtype, W, shape.vocab, shape.eps
+        d.n_layers, d.layers = shape.layers, layers
+        d.n_runs, d.run_layer, d.run_add, d.run_embed = len(order), run_layer, run_add, run_embed
+        d.run_vectors = f32(max(1, shape.loop[2]), W, std=0.1).data_ptr()
+        d.embed = rnd(shape.vocab, W, std=1.0).data_ptr()
+        d.embed_norm, d.final_norm = norm(), norm()
+        d.head = rnd(shape.vocab, W, std=W ** -0.5).data_ptr()
+        d.logit_scale = 0.5
+        d.max_tokens, d.max_seqs, d.page_tokens = max_tokens, max_seqs, page
+        self._desc = (d, layers, run_layer, run_add, run_embed)
+        self.handle = c_void_p()
+        torch.cuda.synchronize()
         _check(self.lib, self.lib.kllm_seq_create(ctypes.byref(d), None, ctypes.byref(self.handle)), "kllm_seq_create")
 
     def open(self):

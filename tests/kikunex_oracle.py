@@ -24,6 +24,7 @@ def rms_unit(x, eps):
 
 def scalar_norm(x, g, eps):
     """RMS norm whose weight is one number."""
+    assert np.ndim(g) == 0
     return rms_unit(x, eps) * float(g)
 
 
@@ -232,7 +233,7 @@ def make_config(width=48, vocab=61, layers=(), loop=None, eps=1e-5, logit_scale=
 def bf16_round(a):
     u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
     u = ((u + 0x7fff + ((u >> 16) & 1)) >> 16) << 16
-    return u.astype(np.uint32).view(np.float32).astype(np.float64)
+    return u.astype(np.uint32).view(np.float32).astype(np.float64).reshape(np.shape(a))
 
 
 def make_weights(cfg, seed=0, sharp=1.0):
