@@ -86,7 +86,7 @@ __device__ __forceinline__ float quad_sum(float v) {
 }
 
 template <int DIM, int VDIM>
-__global__ void __launch_bounds__(kThreads, (DIM + VDIM <= 128) ? 4 : 0)
+__global__ void __launch_bounds__(kThreads, (DIM + VDIM <= 128) ? 4 : (DIM > 128 ? 1 : 0))
 attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV kv, const int32_t* __restrict__ ent_first,
                      const int32_t* __restrict__ ent_count, const int32_t* __restrict__ ent_seq,
                      const int32_t* __restrict__ ent_pos0, int splits, float* __restrict__ ws,
@@ -107,8 +107,11 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
   const int rows_here = min(kRows, n_rows - r0);
   const int pmax = pos0 + (r0 + rows_here - 1) / rep;  // last position any row of the tile sees
   const int n_tiles = pmax / kKeys + 1;
-  const int per = (n_tiles + splits - 1) / splits;
-  const int tile_lo = split * per, tile_hi = min(n_tiles, tile_lo + per);
+  // with a window the first row of the tile sees nothing before its position - window + 1
+  const int window = a.window;
+  const int tile_first = window > 0 ? max(0, pos0 + r0 / rep - window + 1) / kKeys : 0;
+  const int per = (n_tiles - tile_first + splits - 1) / splits;
+  const int tile_lo = tile_first + split * per, tile_hi = min(n_tiles, tile_lo + per);
 
   extern __shared__ __align__(16) unsigned char sm_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(sm_raw);  // [2][keys][LDK]
@@ -156,17 +159,19 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
     const int j = tid >> 1, kj = tile * kKeys + j;
     const bool valid = kj <= pmax;
     size_t slot = 0;
-    if (valid) slot = static_cast<size_t>(table[kj / kv.page]) * kv.page + kj % kv.page;
+    // no page table: the keys and values are the step's own rows, row of position p = first + p - pos0
+    if (valid) slot = kv.table ? static_cast<size_t>(table[kj / kv.page]) * kv.page + kj % kv.page
+                               : static_cast<size_t>(first + max(kj - pos0, 0));
 #pragma unroll
     for (int c = (tid & 1); c < KC + VC; c += 2) {
       if (c < KC) {
         const bool in = valid && c * 8 < dim;
         cp_async16(ks_addr + ((stage * kKeys + j) * LDK + c * 8) * 2,
-                   in ? kbase + (slot * a.kv_heads + g) * dim + c * 8 : kbase, in);
+                   in ? kbase + slot * kv.k_row + g * dim + c * 8 : kbase, in);
       } else {
         const bool in = valid && (c - KC) * 8 < vdim;
         cp_async16(vs_addr + ((stage * kKeys + j) * LDV + (c - KC) * 8) * 2,
-                   in ? vbase + (slot * a.kv_heads + g) * vdim + (c - KC) * 8 : vbase, in);
+                   in ? vbase + slot * kv.v_row + g * vdim + (c - KC) * 8 : vbase, in);
       }
     }
     cp_async_commit();
@@ -183,7 +188,8 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
     }
     __syncthreads();
     const int k0 = tile * kKeys;
-    if (k0 <= warp_last) {  // otherwise no row of this warp sees a key of the tile
+    // otherwise no row of this warp sees a key of the tile (all later, or all before every row's window)
+    if (k0 <= warp_last && (window == 0 || k0 + kKeys - 1 > warp_first - window)) {
       float s[kKeys / 8][4];
 #pragma unroll
       for (int j = 0; j < kKeys / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -202,7 +208,7 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
           }
       }
       float mxA = -INFINITY, mxB = -INFINITY;
-      if (k0 + kKeys - 1 <= warp_first) {  // every row of the warp sees the whole tile
+      if (k0 + kKeys - 1 <= warp_first && (window == 0 || warp_last - k0 < window)) {  // every row of the warp sees the whole tile
 #pragma unroll
         for (int j = 0; j < kKeys / 8; ++j) {
           s[j][0] *= scale2, s[j][1] *= scale2, s[j][2] *= scale2, s[j][3] *= scale2;
@@ -213,10 +219,11 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
 #pragma unroll
         for (int j = 0; j < kKeys / 8; ++j) {
           const int kj = k0 + j * 8 + t4 * 2;
-          s[j][0] = kj <= posA ? s[j][0] * scale2 : -INFINITY;
-          s[j][1] = kj + 1 <= posA ? s[j][1] * scale2 : -INFINITY;
-          s[j][2] = kj <= posB ? s[j][2] * scale2 : -INFINITY;
-          s[j][3] = kj + 1 <= posB ? s[j][3] * scale2 : -INFINITY;
+          const int loA = window > 0 ? posA - window : -1, loB = window > 0 ? posB - window : -1;  // the last key not seen
+          s[j][0] = kj <= posA && kj > loA ? s[j][0] * scale2 : -INFINITY;
+          s[j][1] = kj + 1 <= posA && kj + 1 > loA ? s[j][1] * scale2 : -INFINITY;
+          s[j][2] = kj <= posB && kj > loB ? s[j][2] * scale2 : -INFINITY;
+          s[j][3] = kj + 1 <= posB && kj + 1 > loB ? s[j][3] * scale2 : -INFINITY;
           mxA = fmaxf(mxA, fmaxf(s[j][0], s[j][1]));
           mxB = fmaxf(mxB, fmaxf(s[j][2], s[j][3]));
         }
@@ -268,6 +275,11 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
   }
   lA = quad_sum(lA), lB = quad_sum(lB);
   if (splits == 1) {
+    if (a.sink != nullptr) {  // exp(sink) joins the denominator; scores are in units of log2
+      constexpr float kLog2e = 1.4426950408889634f;
+      if (exA) lA = mA > -INFINITY ? lA + exp2_approx(a.sink[thA % a.heads] * kLog2e - mA) : 1.0f;
+      if (exB) lB = mB > -INFINITY ? lB + exp2_approx(a.sink[thB % a.heads] * kLog2e - mB) : 1.0f;
+    }
     const float gA = exA && gates ? gates[thA] : 1.0f, gB = exB && gates ? gates[thB] : 1.0f;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
@@ -325,9 +337,9 @@ int launch_mma(const AttnShape& a, const void* q, const float* gates, const Page
 
 bool attention_mma_usable(int dtype, const AttnShape& a, int max_count) {
   if (dtype != KLLM_SEQ_BF16 || a.kv_heads <= 0 || a.heads % a.kv_heads) return false;
-  // windows, sinks and fp32 queries / outputs are the split-key kernel's
-  if (a.window > 0 || a.sink != nullptr || a.q_f32 || a.out_f32) return false;
-  const bool dims = a.dim % 8 == 0 && a.dim <= 128 && a.vdim % 8 == 0 && a.vdim <= 128;
+  // fp32 queries / outputs are the split-key kernel's
+  if (a.q_f32 || a.out_f32) return false;
+  const bool dims = a.dim % 8 == 0 && a.dim <= 256 && a.vdim % 8 == 0 && a.vdim <= 128;
   // steps of single tokens keep the split-key kernel (and stay capturable: no attribute call on their path)
   return dims && max_count >= 2 && max_count * (a.heads / a.kv_heads) >= 16;
 }
@@ -343,6 +355,7 @@ int launch_attention_mma(const AttnShape& a, const void* q, const float* gates, 
   KLLM_MMA(64, 128);
   KLLM_MMA(128, 64);
   KLLM_MMA(128, 128);
+  KLLM_MMA(256, 128);
 #undef KLLM_MMA
   return KLLM_E_UNSUPPORTED;
 }

@@ -102,6 +102,7 @@ struct kllm_seq_engine {
   int32_t* pinned = nullptr;
   size_t pinned_cap = 0;
   DevBuf idx, x, h, proj, q, gates, att, y, y2, ws, top_idx, top_w, sgate, inter, pairs_out, sort, sorted_a, sorted_inter, hw, logits, amax;
+  DevBuf lat_c, lat_kr, lat_kp, lat_vp, lat_q, lat_k, lat_v;  // a prompt step's latents expanded into per-head keys / values
   DevBuf x0, hn, qf, qa, ol;  // embedding output; fp32 normed rows ahead of a token shift; latent / linear attention scratch
   float* logits_pinned = nullptr;
   size_t logits_pinned_cap = 0;
@@ -484,6 +485,9 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
     else continue;
     ws_bytes = std::max(ws_bytes, attention_workspace_bytes(a, T, splits));
   }
+  for (const kllm_seq_layer& L : e->layers)  // the chunk sums of linear attention share the attention workspace
+    if (L.mixer_kind == KLLM_SEQ_MIXER_LINEAR)
+      ws_bytes = std::max(ws_bytes, linear_attention_scratch_bytes(L.linear.heads, L.linear.dim, L.linear.vdim, T, n_entries, max_count));
   RC(e->ws.reserve(ws_bytes));
   const bool grouped = T >= kGroupedMinTokens;
   if (e->max_top > 0) {
@@ -504,7 +508,11 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   float* y2 = static_cast<float*>(e->y2.p);
   const bool tracing = e->trace_host != nullptr;
   bool single = true;  // every entry brings one token: a row's CTA owns its sequence's state
-  for (int i = 0; i < n_entries; ++i) single = single && counts[i] == 1;
+  bool fresh_prompt = getenv("KLLM_SEQ_LATENT_EXPAND") == nullptr || getenv("KLLM_SEQ_LATENT_EXPAND")[0] != '0';
+  for (int i = 0; i < n_entries; ++i) {
+    single = single && counts[i] == 1;
+    fresh_prompt = fresh_prompt && h_pos0[i] == 0;  // every sequence starts with this step
+  }
 
   // ---- device: the layer runs -------------------------------------------------------------------------------------
   e->prof_used = 0;
@@ -564,7 +572,37 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       float* gates = static_cast<float*>(e->gates.p);
       RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, A.q_rank + krow + A.heads, st));
       e->mark(KLLM_SEQ_PHASE_IN_PROJ);
-      RC(launch_latent_prepare(dtype, ls, proj, A.q_norm_w, A.kv_norm_w, d.norm_eps, d_seq, d_pos, e->q.p, gates, kv, T, st));
+      // Prompt steps whose sequences all start here: the step's own latents are all the keys there are, so they are
+      // expanded into per-head keys and values (two products) and the tensor-core attention runs on those rows.  Every
+      // other step scores against the cached latents (the absorbed form below).
+      const int dqk = A.dim + A.rot_dim;
+      const AttnShape eshape{A.heads, A.heads, dqk, A.vdim, A.scale, 0.f, 0, 0, 1, A.window, A.sink, 0, 0};
+      if (fresh_prompt && attention_mma_usable(dtype, eshape, max_count)) {
+        RC(e->lat_c.reserve(Ts * A.kv_rank * es));
+        RC(e->lat_kr.reserve(Ts * std::max(1, A.rot_dim) * 4));
+        RC(e->lat_kp.reserve(Ts * A.heads * A.dim * 4));
+        RC(e->lat_vp.reserve(Ts * A.heads * A.vdim * 4));
+        RC(e->lat_q.reserve(Ts * A.heads * dqk * es));
+        RC(e->lat_k.reserve(Ts * A.heads * dqk * es));
+        RC(e->lat_v.reserve(Ts * A.heads * A.vdim * es));
+        RC(launch_latent_prepare(dtype, ls, proj, A.q_norm_w, A.kv_norm_w, d.norm_eps, d_seq, d_pos, e->q.p, gates, kv,
+                                 e->lat_c.p, static_cast<float*>(e->lat_kr.p), T, st));
+        RC(gemm(dtype, e->q.p, A.w_uq, static_cast<float*>(e->qf.p), T, A.q_rank, A.heads * dqk, st));
+        RC(launch_latent_pack_q(dtype, ls, static_cast<const float*>(e->qf.p), d_pos, e->lat_q.p, T, st));
+        RC(gemm(dtype, e->lat_c.p, A.w_uk, static_cast<float*>(e->lat_kp.p), T, A.kv_rank, A.heads * A.dim, st));
+        RC(gemm(dtype, e->lat_c.p, A.w_uv, static_cast<float*>(e->lat_vp.p), T, A.kv_rank, A.heads * A.vdim, st));
+        RC(launch_latent_pack_kv(dtype, ls, static_cast<const float*>(e->lat_kp.p), static_cast<const float*>(e->lat_kr.p),
+                                 static_cast<const float*>(e->lat_vp.p), e->lat_k.p, e->lat_v.p, T, st));
+        e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
+        const PagedKV rows{e->lat_k.p, e->lat_v.p, nullptr, 0, 1, A.heads * dqk, A.heads * A.vdim};
+        RC(launch_attention(dtype, eshape, e->lat_q.p, gates, rows, n_entries, d_first, d_count, d_eseq, d_pos0, max_count,
+                            max_ctx, 1, static_cast<float*>(e->ws.p), e->att.p, T, d_seq, d_pos, st));
+        e->mark(KLLM_SEQ_PHASE_ATTENTION);
+        RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
+        e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
+      } else {
+      RC(launch_latent_prepare(dtype, ls, proj, A.q_norm_w, A.kv_norm_w, d.norm_eps, d_seq, d_pos, e->q.p, gates, kv, nullptr,
+                               nullptr, T, st));
       RC(gemm(dtype, e->q.p, A.w_uq, static_cast<float*>(e->qf.p), T, A.q_rank, A.heads * (A.dim + A.rot_dim), st));
       RC(launch_latent_absorb(dtype, ls, static_cast<const float*>(e->qf.p), A.w_uk, d_pos, static_cast<float*>(e->qa.p), T, st));
       e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
@@ -576,12 +614,13 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       e->mark(KLLM_SEQ_PHASE_ATTENTION);
       RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
       e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
+      }
     } else {
       const kllm_seq_linear& A = L.linear;
       RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, 2 * A.heads * (A.dim + A.vdim), st));
       e->mark(KLLM_SEQ_PHASE_IN_PROJ);
       RC(launch_linear_attention(A.heads, A.dim, A.vdim, A.decay, proj, e->linear_state[r], n_entries, d_first, d_count,
-                                 d_eseq, d_pos0, max_count, static_cast<float*>(e->ol.p), st));
+                                 d_eseq, d_pos0, max_count, static_cast<float*>(e->ws.p), static_cast<float*>(e->ol.p), st));
       RC(launch_linear_out(dtype, A.heads, A.dim, A.vdim, static_cast<const float*>(e->ol.p), proj, A.out_norm_w, d.norm_eps,
                            e->att.p, T, st));
       e->mark(KLLM_SEQ_PHASE_ATTENTION);

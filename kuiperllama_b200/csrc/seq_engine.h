@@ -146,7 +146,15 @@ struct LatentShape {
 // [kv_rank normed latent | rot_dim rotated key part] of every token, gates [T, heads] = sigmoid
 int launch_latent_prepare(int dtype, const LatentShape& a, const float* proj, const float* q_norm_w, const float* kv_norm_w,
                           float eps, const int32_t* tok_seq, const int32_t* tok_pos, void* cq, float* gates,
-                          const PagedKV& kv, int T, cudaStream_t s);
+                          const PagedKV& kv, void* c_rows, float* kr_rows, int T, cudaStream_t s);
+// Prompt steps that start their sequences can expand the latents of the step into per-head keys and values and run the
+// tensor-core attention on them: c_rows [T, kv_rank] (compute type) and kr_rows [T, rot_dim] (fp32, rotated) are the
+// step's latents as rows (optional outputs of latent_prepare); pack_q rotates and converts the queries; pack_kv joins
+// W_uk c with the shared rotated part and converts W_uv c.
+int launch_latent_pack_q(int dtype, const LatentShape& a, const float* q, const int32_t* tok_pos, void* out, int T,
+                         cudaStream_t s);
+int launch_latent_pack_kv(int dtype, const LatentShape& a, const float* kp, const float* kr, const float* vp, void* k, void* v,
+                          int T, cudaStream_t s);
 // q [T, heads, dim + rot_dim] fp32 -> qa [T, heads, kv_rank + rot_dim] fp32: W_uk(head)^T q_plain | rotated q_rot
 int launch_latent_absorb(int dtype, const LatentShape& a, const float* q, const void* w_uk, const int32_t* tok_pos, float* qa,
                          int T, cudaStream_t s);
@@ -156,9 +164,11 @@ int launch_latent_expand(int dtype, const LatentShape& a, const float* ol, const
 // proj [T, 2 * heads * dim + 2 * heads * vdim] fp32: q | k | v | gate rows before their activations.  Runs the recurrence
 // of every entry from its sequence's state ([slots][heads][dim][vdim] fp32; zeros at position 0), writes o [T, heads * vdim]
 // fp32 and the new state.
+// Steps with long entries work chunk-parallel through `scratch` (linear_attention_scratch_bytes(); 0: not needed).
+size_t linear_attention_scratch_bytes(int heads, int dim, int vdim, int T, int n_entries, int max_count);
 int launch_linear_attention(int heads, int dim, int vdim, const float* decay, const float* proj, float* state, int n_entries,
                             const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
-                            const int32_t* ent_pos0, int max_count, float* o, cudaStream_t s);
+                            const int32_t* ent_pos0, int max_count, float* scratch, float* o, cudaStream_t s);
 // out[t] = RMSnorm(o[t]; w) * sigmoid(gate rows of proj[t]) in the compute type
 int launch_linear_out(int dtype, int heads, int dim, int vdim, const float* o, const float* proj, const float* norm_w, float eps,
                       void* out, int T, cudaStream_t s);

@@ -64,7 +64,7 @@ template <typename AT>
 __global__ void latent_prepare_kernel(LatentShape a, const float* __restrict__ proj, const float* __restrict__ q_norm_w,
                                       const float* __restrict__ kv_norm_w, float eps, const int32_t* __restrict__ tok_seq,
                                       const int32_t* __restrict__ tok_pos, AT* __restrict__ cq, float* __restrict__ gates,
-                                      PagedKV kv) {
+                                      PagedKV kv, AT* __restrict__ c_rows, float* __restrict__ kr_rows) {
   __shared__ float red[33];
   const int t = blockIdx.x;
   const int stride = a.q_rank + a.kv_rank + a.rot_dim + a.heads;
@@ -81,10 +81,17 @@ __global__ void latent_prepare_kernel(LatentShape a, const float* __restrict__ p
   const float rc = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(a.kv_rank) + eps);
   const int page = kv.table[static_cast<size_t>(seq) * kv.table_stride + pos / kv.page];
   AT* dst = static_cast<AT*>(kv.k) + (static_cast<size_t>(page) * kv.page + pos % kv.page) * kv.k_row;
-  for (int i = threadIdx.x; i < a.kv_rank; i += blockDim.x) dst[i] = from_f<AT>(c[i] * rc * kv_norm_w[i]);
+  for (int i = threadIdx.x; i < a.kv_rank; i += blockDim.x) {
+    const AT v = from_f<AT>(c[i] * rc * kv_norm_w[i]);
+    dst[i] = v;
+    if (c_rows) c_rows[static_cast<size_t>(t) * a.kv_rank + i] = v;
+  }
   const float* kr = c + a.kv_rank;
-  for (int i = threadIdx.x; i < a.rot_dim; i += blockDim.x)
-    dst[a.kv_rank + i] = from_f<AT>(rotated(kr, i, a.rope_dims, a.rope_base, pos));
+  for (int i = threadIdx.x; i < a.rot_dim; i += blockDim.x) {
+    const float v = rotated(kr, i, a.rope_dims, a.rope_base, pos);
+    dst[a.kv_rank + i] = from_f<AT>(v);
+    if (kr_rows) kr_rows[static_cast<size_t>(t) * a.rot_dim + i] = v;
+  }
   const float* g = kr + a.rot_dim;
   for (int h = threadIdx.x; h < a.heads; h += blockDim.x) gates[static_cast<size_t>(t) * a.heads + h] = sigmoidf(g[h]);
 }
@@ -122,6 +129,36 @@ __global__ void latent_absorb_kernel(LatentShape a, const float* __restrict__ q,
     qa[(static_cast<size_t>(t0 + j) * a.heads + h) * dl + a.kv_rank + c] =
         rotated(qs + j * dq + a.dim, c, a.rope_dims, a.rope_base, tok_pos[t0 + j]);
   }
+}
+
+// ---- latent attention with per-head keys and values (prompt steps on the tensor cores) ---------------------------------------
+// q [T, heads, dim + rot_dim] fp32 -> the same in the compute type with the rotated part rotated
+template <typename AT>
+__global__ void latent_pack_q_kernel(LatentShape a, const float* __restrict__ q, const int32_t* __restrict__ tok_pos,
+                                     AT* __restrict__ out) {
+  const int t = blockIdx.x, dq = a.dim + a.rot_dim;
+  const int pos = tok_pos[t];
+  const float* row = q + static_cast<size_t>(t) * a.heads * dq;
+  for (int i = threadIdx.x; i < a.heads * dq; i += blockDim.x) {
+    const int h = i / dq, d = i % dq;
+    const float v = d < a.dim ? row[i] : rotated(row + h * dq + a.dim, d - a.dim, a.rope_dims, a.rope_base, pos);
+    out[static_cast<size_t>(t) * a.heads * dq + i] = from_f<AT>(v);
+  }
+}
+// kp [T, heads * dim] fp32 (W_uk c) and kr [T, rot_dim] (rotated, shared by the heads) -> k [T, heads, dim + rot_dim];
+// vp [T, heads * vdim] fp32 (W_uv c) -> v, both in the compute type
+template <typename AT>
+__global__ void latent_pack_kv_kernel(LatentShape a, const float* __restrict__ kp, const float* __restrict__ kr,
+                                      const float* __restrict__ vp, AT* __restrict__ k, AT* __restrict__ v) {
+  const int t = blockIdx.x, dq = a.dim + a.rot_dim;
+  for (int i = threadIdx.x; i < a.heads * dq; i += blockDim.x) {
+    const int h = i / dq, d = i % dq;
+    const float x = d < a.dim ? kp[(static_cast<size_t>(t) * a.heads + h) * a.dim + d]
+                              : kr[static_cast<size_t>(t) * a.rot_dim + d - a.dim];
+    k[static_cast<size_t>(t) * a.heads * dq + i] = from_f<AT>(x);
+  }
+  for (int i = threadIdx.x; i < a.heads * a.vdim; i += blockDim.x)
+    v[static_cast<size_t>(t) * a.heads * a.vdim + i] = from_f<AT>(vp[static_cast<size_t>(t) * a.heads * a.vdim + i]);
 }
 
 // ---- latent attention: weighted sums of latents -> per-head values ---------------------------------------------------------
@@ -166,6 +203,7 @@ __global__ void latent_expand_kernel(LatentShape a, const float* __restrict__ ol
 constexpr int kLinChunk = 32;
 constexpr int kLinCols = 32;
 constexpr int kLinThreads = 128;
+constexpr int kLinParallelFrom = 2 * kLinChunk;  // steps whose longest entry has more tokens take the chunk-parallel kernels
 
 __global__ void __launch_bounds__(kLinThreads)
 linear_attention_kernel(int heads, int dim, int vdim, const float* __restrict__ decay, const float* __restrict__ proj,
@@ -242,6 +280,132 @@ linear_attention_kernel(int heads, int dim, int vdim, const float* __restrict__ 
   }
 }
 
+// ---- linear attention over long entries: chunks in parallel ---------------------------------------------------------------
+// The recurrence above is sequential only in the state.  For entries of many chunks it is cut into three kernels:
+//   linear_chunk_sums_kernel   every chunk on its own: U_c = sum_j l^(n-1-j) k_j v_j^T                       (parallel)
+//   linear_scan_kernel         S_before(c) in place of U_c, chunk after chunk: S <- l^n S + U_c; the final state  (per element)
+//   linear_chunk_out_kernel    every chunk on its own: o_i = l^(i+1) S_before^T q_i + decayed scores inside the chunk
+// Chunk j of entry e lives in slot (first_e + j * chunk) / chunk + e of the scratch buffer [slots][heads][dim][vdim].
+__device__ __forceinline__ size_t chunk_slot(int first, int base, int e) { return static_cast<size_t>((first + base) / kLinChunk + e); }
+
+__global__ void __launch_bounds__(kLinThreads)
+linear_chunk_sums_kernel(int heads, int dim, int vdim, const float* __restrict__ decay, const float* __restrict__ proj,
+                         const int32_t* __restrict__ ent_first, const int32_t* __restrict__ ent_count,
+                         float* __restrict__ sums) {
+  extern __shared__ float sm[];
+  const int e = blockIdx.z, h = blockIdx.y;
+  const int n_slices = (vdim + kLinCols - 1) / kLinCols;
+  const int chunk = blockIdx.x / n_slices, c0 = (blockIdx.x % n_slices) * kLinCols;
+  const int count = ent_count[e], first = ent_first[e], base = chunk * kLinChunk;
+  if (base >= count) return;
+  const int n = min(kLinChunk, count - base);
+  const int cols = min(kLinCols, vdim - c0);
+  const int dp = dim + 1;
+  float* Ks = sm;                       // [chunk][dp], already times l^(n-1-j)
+  float* Vs = Ks + kLinChunk * dp;      // [chunk][kLinCols]
+  const int tid = threadIdx.x;
+  const float llog = logf(decay[h]);
+  const int qn = heads * dim, vn = heads * vdim, stride = 2 * qn + 2 * vn;
+  for (int i = tid; i < n * dim; i += kLinThreads) {
+    const int j = i / dim, d = i % dim;
+    const float w = n - 1 - j == 0 ? 1.0f : expf(llog * static_cast<float>(n - 1 - j));
+    Ks[j * dp + d] = siluf(proj[static_cast<size_t>(first + base + j) * stride + qn + h * dim + d]) * w;
+  }
+  for (int i = tid; i < n * kLinCols; i += kLinThreads) {
+    const int j = i / kLinCols, c = i % kLinCols;
+    Vs[i] = c < cols ? siluf(proj[static_cast<size_t>(first + base + j) * stride + 2 * qn + h * vdim + c0 + c]) : 0.f;
+  }
+  __syncthreads();
+  float* out = sums + (chunk_slot(first, base, e) * heads + h) * dim * vdim;
+  for (int i = tid; i < dim * kLinCols; i += kLinThreads) {
+    const int d = i / kLinCols, c = i % kLinCols;
+    float acc = 0.f;
+    for (int j = 0; j < n; ++j) acc = fmaf(Ks[j * dp + d], Vs[j * kLinCols + c], acc);
+    if (c < cols) out[static_cast<size_t>(d) * vdim + c0 + c] = acc;
+  }
+}
+
+__global__ void linear_scan_kernel(int heads, int dim, int vdim, const float* __restrict__ decay, float* __restrict__ state,
+                                   const int32_t* __restrict__ ent_first, const int32_t* __restrict__ ent_count,
+                                   const int32_t* __restrict__ ent_seq, const int32_t* __restrict__ ent_pos0,
+                                   float* __restrict__ sums) {
+  const int e = blockIdx.z, h = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= dim * vdim) return;
+  const int count = ent_count[e], first = ent_first[e];
+  const float llog = logf(decay[h]);
+  const float full = expf(llog * static_cast<float>(kLinChunk));
+  float* sg = state + (static_cast<size_t>(ent_seq[e]) * heads + h) * dim * vdim + i;
+  float s = ent_pos0[e] == 0 ? 0.f : *sg;
+  for (int base = 0; base < count; base += kLinChunk) {
+    const int n = min(kLinChunk, count - base);
+    float* u = sums + (chunk_slot(first, base, e) * heads + h) * dim * vdim + i;
+    const float add = *u;
+    *u = s;
+    s = fmaf(s, n == kLinChunk ? full : expf(llog * static_cast<float>(n)), add);
+  }
+  *sg = s;
+}
+
+__global__ void __launch_bounds__(kLinThreads)
+linear_chunk_out_kernel(int heads, int dim, int vdim, const float* __restrict__ decay, const float* __restrict__ proj,
+                        const int32_t* __restrict__ ent_first, const int32_t* __restrict__ ent_count,
+                        const float* __restrict__ sums, float* __restrict__ o) {
+  extern __shared__ float sm[];
+  const int e = blockIdx.z, h = blockIdx.y;
+  const int n_slices = (vdim + kLinCols - 1) / kLinCols;
+  const int chunk = blockIdx.x / n_slices, c0 = (blockIdx.x % n_slices) * kLinCols;
+  const int count = ent_count[e], first = ent_first[e], base = chunk * kLinChunk;
+  if (base >= count) return;
+  const int n = min(kLinChunk, count - base);
+  const int cols = min(kLinCols, vdim - c0);
+  const int dp = dim + 1;
+  float* Qs = sm;
+  float* Ks = Qs + kLinChunk * dp;
+  float* Vs = Ks + kLinChunk * dp;
+  float* As = Vs + kLinChunk * kLinCols;
+  float* Ss = As + kLinChunk * (kLinChunk + 1);
+  float* pw = Ss + dim * kLinCols;
+  const int tid = threadIdx.x;
+  const float llog = logf(decay[h]);
+  if (tid <= kLinChunk) pw[tid] = tid == 0 ? 1.0f : expf(llog * static_cast<float>(tid));
+  const float* sb = sums + (chunk_slot(first, base, e) * heads + h) * dim * vdim;
+  for (int i = tid; i < dim * kLinCols; i += kLinThreads) {
+    const int d = i / kLinCols, c = i % kLinCols;
+    Ss[i] = c < cols ? sb[static_cast<size_t>(d) * vdim + c0 + c] : 0.f;
+  }
+  const int qn = heads * dim, vn = heads * vdim, stride = 2 * qn + 2 * vn;
+  for (int i = tid; i < n * dim; i += kLinThreads) {
+    const int j = i / dim, d = i % dim;
+    const float* row = proj + static_cast<size_t>(first + base + j) * stride;
+    Qs[j * dp + d] = siluf(row[h * dim + d]);
+    Ks[j * dp + d] = siluf(row[qn + h * dim + d]);
+  }
+  for (int i = tid; i < n * kLinCols; i += kLinThreads) {
+    const int j = i / kLinCols, c = i % kLinCols;
+    Vs[i] = c < cols ? siluf(proj[static_cast<size_t>(first + base + j) * stride + 2 * qn + h * vdim + c0 + c]) : 0.f;
+  }
+  __syncthreads();
+  for (int i = tid; i < n * n; i += kLinThreads) {
+    const int r = i / n, j = i % n;
+    float acc = 0.f;
+    if (j <= r) {
+      for (int d = 0; d < dim; ++d) acc = fmaf(Qs[r * dp + d], Ks[j * dp + d], acc);
+      acc *= pw[r - j];
+    }
+    As[r * (kLinChunk + 1) + j] = acc;
+  }
+  __syncthreads();
+  for (int i = tid; i < n * kLinCols; i += kLinThreads) {
+    const int r = i / kLinCols, c = i % kLinCols;
+    float carry = 0.f;
+    for (int d = 0; d < dim; ++d) carry = fmaf(Qs[r * dp + d], Ss[d * kLinCols + c], carry);
+    float acc = carry * pw[r + 1];
+    for (int j = 0; j <= r; ++j) acc = fmaf(As[r * (kLinChunk + 1) + j], Vs[j * kLinCols + c], acc);
+    if (c < cols) o[static_cast<size_t>(first + base + r) * vn + h * vdim + c0 + c] = acc;
+  }
+}
+
 template <typename AT>
 __global__ void linear_out_kernel(int qn, int vn, const float* __restrict__ o, const float* __restrict__ proj,
                                   const float* __restrict__ norm_w, float eps, AT* __restrict__ out) {
@@ -294,9 +458,23 @@ inline int done() {
 
 int launch_latent_prepare(int dtype, const LatentShape& a, const float* proj, const float* q_norm_w, const float* kv_norm_w,
                           float eps, const int32_t* tok_seq, const int32_t* tok_pos, void* cq, float* gates,
-                          const PagedKV& kv, int T, cudaStream_t s) {
+                          const PagedKV& kv, void* c_rows, float* kr_rows, int T, cudaStream_t s) {
   KLLM_SEQ_DISPATCH(dtype, (latent_prepare_kernel<AT><<<T, 128, 0, s>>>(a, proj, q_norm_w, kv_norm_w, eps, tok_seq, tok_pos,
-                                                                       static_cast<AT*>(cq), gates, kv)));
+                                                                       static_cast<AT*>(cq), gates, kv,
+                                                                       static_cast<AT*>(c_rows), kr_rows)));
+  return done();
+}
+
+int launch_latent_pack_q(int dtype, const LatentShape& a, const float* q, const int32_t* tok_pos, void* out, int T,
+                         cudaStream_t s) {
+  KLLM_SEQ_DISPATCH(dtype, (latent_pack_q_kernel<AT><<<T, 256, 0, s>>>(a, q, tok_pos, static_cast<AT*>(out))));
+  return done();
+}
+
+int launch_latent_pack_kv(int dtype, const LatentShape& a, const float* kp, const float* kr, const float* vp, void* k, void* v,
+                          int T, cudaStream_t s) {
+  KLLM_SEQ_DISPATCH(dtype, (latent_pack_kv_kernel<AT><<<T, 256, 0, s>>>(a, kp, kr, vp, static_cast<AT*>(k),
+                                                                       static_cast<AT*>(v))));
   return done();
 }
 
@@ -320,10 +498,14 @@ int launch_latent_expand(int dtype, const LatentShape& a, const float* ol, const
   return done();
 }
 
+size_t linear_attention_scratch_bytes(int heads, int dim, int vdim, int T, int n_entries, int max_count) {
+  if (max_count <= kLinParallelFrom) return 0;
+  return (static_cast<size_t>(T) / kLinChunk + n_entries + 1) * heads * dim * vdim * sizeof(float);
+}
+
 int launch_linear_attention(int heads, int dim, int vdim, const float* decay, const float* proj, float* state, int n_entries,
                             const int32_t* ent_first, const int32_t* ent_count, const int32_t* ent_seq,
-                            const int32_t* ent_pos0, int max_count, float* o, cudaStream_t s) {
-  (void)max_count;
+                            const int32_t* ent_pos0, int max_count, float* scratch, float* o, cudaStream_t s) {
   const size_t smem = (2 * static_cast<size_t>(kLinChunk) * (dim + 1) + kLinChunk * kLinCols + kLinChunk * (kLinChunk + 1) +
                        static_cast<size_t>(dim) * kLinCols + kLinChunk + 1) * sizeof(float);
   if (smem > 200 * 1024) return KLLM_E_UNSUPPORTED;
@@ -333,6 +515,26 @@ int launch_linear_attention(int heads, int dim, int vdim, const float* decay, co
                                                static_cast<int>(smem));
     if (e != cudaSuccess) return cuda_rc(e);
     configured = smem;
+  }
+  if (max_count > kLinParallelFrom && scratch != nullptr) {  // long entries: chunks in parallel
+    static size_t configured_out = 0;
+    if (smem > 48 * 1024 && smem > configured_out) {
+      cudaError_t e = cudaFuncSetAttribute(linear_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(linear_chunk_sums_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return cuda_rc(e);
+      configured_out = smem;
+    }
+    const int n_slices = (vdim + kLinCols - 1) / kLinCols, chunks = (max_count + kLinChunk - 1) / kLinChunk;
+    const dim3 grid(chunks * n_slices, heads, n_entries);
+    const size_t smem_sums = (static_cast<size_t>(kLinChunk) * (dim + 1) + kLinChunk * kLinCols) * sizeof(float);
+    linear_chunk_sums_kernel<<<grid, kLinThreads, smem_sums, s>>>(heads, dim, vdim, decay, proj, ent_first, ent_count, scratch);
+    count_launch();
+    const dim3 sgrid((dim * vdim + 127) / 128, heads, n_entries);
+    linear_scan_kernel<<<sgrid, 128, 0, s>>>(heads, dim, vdim, decay, state, ent_first, ent_count, ent_seq, ent_pos0, scratch);
+    count_launch();
+    linear_chunk_out_kernel<<<grid, kLinThreads, smem, s>>>(heads, dim, vdim, decay, proj, ent_first, ent_count, scratch, o);
+    return done();
   }
   const dim3 grid((vdim + kLinCols - 1) / kLinCols, heads, n_entries);
   linear_attention_kernel<<<grid, kLinThreads, smem, s>>>(heads, dim, vdim, decay, proj, state, ent_first, ent_count, ent_seq,
