@@ -337,21 +337,37 @@ __global__ void linear_scan_kernel(int heads, int dim, int vdim, const float* __
   const float full = expf(llog * static_cast<float>(kLinChunk));
   float* sg = state + (static_cast<size_t>(ent_seq[e]) * heads + h) * dim * vdim + i;
   float s = ent_pos0[e] == 0 ? 0.f : *sg;
-  for (int base = 0; base < count; base += kLinChunk) {
-    const int n = min(kLinChunk, count - base);
-    float* u = sums + (chunk_slot(first, base, e) * heads + h) * dim * vdim + i;
-    const float add = *u;
-    *u = s;
-    s = fmaf(s, n == kLinChunk ? full : expf(llog * static_cast<float>(n)), add);
+  // the chunk sums are fetched eight chunks ahead: the loads do not depend on one another, only the sums do
+  constexpr int U = 8;
+  for (int base = 0; base < count; base += U * kLinChunk) {
+    float add[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int b = base + u * kLinChunk;
+      add[u] = b < count ? sums[(chunk_slot(first, b, e) * heads + h) * dim * vdim + i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int b = base + u * kLinChunk;
+      if (b >= count) break;
+      const int n = min(kLinChunk, count - b);
+      sums[(chunk_slot(first, b, e) * heads + h) * dim * vdim + i] = s;
+      s = fmaf(s, n == kLinChunk ? full : expf(llog * static_cast<float>(n)), add[u]);
+    }
   }
   *sg = s;
 }
+
+// Each thread keeps 8 rows (warp + 4 k) of one column: a 16-byte broadcast load brings four coordinates of a row, so the
+// inner loops issue 12 shared-memory loads for 32 multiply-adds.  Rows and coordinates past the chunk are zero-filled.
+__host__ __device__ inline int lin_dp(int dim) { return ((dim + 3) & ~3) + 4; }  // row stride of Qs / Ks: 16-byte rows, odd in 16-byte units for dim % 8 == 0
+constexpr int kLinAs = kLinChunk + 4;
 
 __global__ void __launch_bounds__(kLinThreads)
 linear_chunk_out_kernel(int heads, int dim, int vdim, const float* __restrict__ decay, const float* __restrict__ proj,
                         const int32_t* __restrict__ ent_first, const int32_t* __restrict__ ent_count,
                         const float* __restrict__ sums, float* __restrict__ o) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   const int e = blockIdx.z, h = blockIdx.y;
   const int n_slices = (vdim + kLinCols - 1) / kLinCols;
   const int chunk = blockIdx.x / n_slices, c0 = (blockIdx.x % n_slices) * kLinCols;
@@ -359,50 +375,87 @@ linear_chunk_out_kernel(int heads, int dim, int vdim, const float* __restrict__ 
   if (base >= count) return;
   const int n = min(kLinChunk, count - base);
   const int cols = min(kLinCols, vdim - c0);
-  const int dp = dim + 1;
-  float* Qs = sm;
-  float* Ks = Qs + kLinChunk * dp;
-  float* Vs = Ks + kLinChunk * dp;
-  float* As = Vs + kLinChunk * kLinCols;
-  float* Ss = As + kLinChunk * (kLinChunk + 1);
-  float* pw = Ss + dim * kLinCols;
-  const int tid = threadIdx.x;
+  const int d4 = (dim + 3) & ~3, dp = lin_dp(dim);
+  float* Qs = sm;                          // [chunk][dp]
+  float* Ks = Qs + kLinChunk * dp;         // [chunk][dp]
+  float* Vs = Ks + kLinChunk * dp;         // [chunk][kLinCols]
+  float* As = Vs + kLinChunk * kLinCols;   // [chunk][kLinAs]
+  float* Ss = As + kLinChunk * kLinAs;     // [d4][kLinCols]
+  float* pw = Ss + d4 * kLinCols;          // [chunk + 1]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float llog = logf(decay[h]);
   if (tid <= kLinChunk) pw[tid] = tid == 0 ? 1.0f : expf(llog * static_cast<float>(tid));
   const float* sb = sums + (chunk_slot(first, base, e) * heads + h) * dim * vdim;
-  for (int i = tid; i < dim * kLinCols; i += kLinThreads) {
+  for (int i = tid; i < d4 * kLinCols; i += kLinThreads) {
     const int d = i / kLinCols, c = i % kLinCols;
-    Ss[i] = c < cols ? sb[static_cast<size_t>(d) * vdim + c0 + c] : 0.f;
+    Ss[i] = (d < dim && c < cols) ? sb[static_cast<size_t>(d) * vdim + c0 + c] : 0.f;
   }
   const int qn = heads * dim, vn = heads * vdim, stride = 2 * qn + 2 * vn;
-  for (int i = tid; i < n * dim; i += kLinThreads) {
-    const int j = i / dim, d = i % dim;
-    const float* row = proj + static_cast<size_t>(first + base + j) * stride;
-    Qs[j * dp + d] = siluf(row[h * dim + d]);
-    Ks[j * dp + d] = siluf(row[qn + h * dim + d]);
-  }
-  for (int i = tid; i < n * kLinCols; i += kLinThreads) {
-    const int j = i / kLinCols, c = i % kLinCols;
-    Vs[i] = c < cols ? siluf(proj[static_cast<size_t>(first + base + j) * stride + 2 * qn + h * vdim + c0 + c]) : 0.f;
-  }
-  __syncthreads();
-  for (int i = tid; i < n * n; i += kLinThreads) {
-    const int r = i / n, j = i % n;
-    float acc = 0.f;
-    if (j <= r) {
-      for (int d = 0; d < dim; ++d) acc = fmaf(Qs[r * dp + d], Ks[j * dp + d], acc);
-      acc *= pw[r - j];
+  for (int i = tid; i < kLinChunk * d4; i += kLinThreads) {
+    const int j = i / d4, d = i % d4;
+    float qv = 0.f, kv = 0.f;
+    if (j < n && d < dim) {
+      const float* row = proj + static_cast<size_t>(first + base + j) * stride;
+      qv = siluf(row[h * dim + d]);
+      kv = siluf(row[qn + h * dim + d]);
     }
-    As[r * (kLinChunk + 1) + j] = acc;
+    Qs[j * dp + d] = qv;
+    Ks[j * dp + d] = kv;
+  }
+  for (int i = tid; i < kLinChunk * kLinCols; i += kLinThreads) {
+    const int j = i / kLinCols, c = i % kLinCols;
+    Vs[i] = (j < n && c < cols) ? siluf(proj[static_cast<size_t>(first + base + j) * stride + 2 * qn + h * vdim + c0 + c]) : 0.f;
   }
   __syncthreads();
-  for (int i = tid; i < n * kLinCols; i += kLinThreads) {
-    const int r = i / kLinCols, c = i % kLinCols;
-    float carry = 0.f;
-    for (int d = 0; d < dim; ++d) carry = fmaf(Qs[r * dp + d], Ss[d * kLinCols + c], carry);
-    float acc = carry * pw[r + 1];
-    for (int j = 0; j <= r; ++j) acc = fmaf(As[r * (kLinChunk + 1) + j], Vs[j * kLinCols + c], acc);
-    if (c < cols) o[static_cast<size_t>(first + base + r) * vn + h * vdim + c0 + c] = acc;
+  constexpr int R = kLinChunk / 4;  // rows per thread
+  {  // decayed scores inside the chunk: lane = key j, rows warp + 4 k
+    float acc[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) acc[k] = 0.f;
+    for (int d = 0; d < d4; d += 4) {
+      const float4 kv = *reinterpret_cast<const float4*>(Ks + lane * dp + d);
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        const float4 qv = *reinterpret_cast<const float4*>(Qs + (warp + 4 * k) * dp + d);
+        acc[k] = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, fmaf(qv.w, kv.w, acc[k]))));
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const int r = warp + 4 * k;
+      As[r * kLinAs + lane] = (lane <= r && r < n) ? acc[k] * pw[r - lane] : 0.f;
+    }
+  }
+  __syncthreads();
+  {  // outputs: lane = column, rows warp + 4 k
+    float acc[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) acc[k] = 0.f;
+    for (int d = 0; d < d4; d += 4) {
+      const float s0 = Ss[d * kLinCols + lane], s1 = Ss[(d + 1) * kLinCols + lane], s2 = Ss[(d + 2) * kLinCols + lane],
+                  s3 = Ss[(d + 3) * kLinCols + lane];
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        const float4 qv = *reinterpret_cast<const float4*>(Qs + (warp + 4 * k) * dp + d);
+        acc[k] = fmaf(qv.x, s0, fmaf(qv.y, s1, fmaf(qv.z, s2, fmaf(qv.w, s3, acc[k]))));
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < R; ++k) acc[k] *= pw[min(warp + 4 * k + 1, kLinChunk)];
+    for (int j = 0; j < kLinChunk; j += 4) {
+      const float v0 = Vs[j * kLinCols + lane], v1 = Vs[(j + 1) * kLinCols + lane], v2 = Vs[(j + 2) * kLinCols + lane],
+                  v3 = Vs[(j + 3) * kLinCols + lane];
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        const float4 av = *reinterpret_cast<const float4*>(As + (warp + 4 * k) * kLinAs + j);
+        acc[k] = fmaf(av.x, v0, fmaf(av.y, v1, fmaf(av.z, v2, fmaf(av.w, v3, acc[k]))));
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const int r = warp + 4 * k;
+      if (r < n && lane < cols) o[static_cast<size_t>(first + base + r) * vn + h * vdim + c0 + lane] = acc[k];
+    }
   }
 }
 
@@ -517,13 +570,16 @@ int launch_linear_attention(int heads, int dim, int vdim, const float* decay, co
     configured = smem;
   }
   if (max_count > kLinParallelFrom && scratch != nullptr) {  // long entries: chunks in parallel
+    const size_t smem_out = (2 * static_cast<size_t>(kLinChunk) * lin_dp(dim) + kLinChunk * kLinCols + kLinChunk * kLinAs +
+                             static_cast<size_t>((dim + 3) & ~3) * kLinCols + kLinChunk + 4) * sizeof(float);
     static size_t configured_out = 0;
-    if (smem > 48 * 1024 && smem > configured_out) {
-      cudaError_t e = cudaFuncSetAttribute(linear_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (smem_out > 48 * 1024 && smem_out > configured_out) {
+      cudaError_t e = cudaFuncSetAttribute(linear_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem_out));
       if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(linear_chunk_sums_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        e = cudaFuncSetAttribute(linear_chunk_sums_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_out));
       if (e != cudaSuccess) return cuda_rc(e);
-      configured_out = smem;
+      configured_out = smem_out;
     }
     const int n_slices = (vdim + kLinCols - 1) / kLinCols, chunks = (max_count + kLinChunk - 1) / kLinChunk;
     const dim3 grid(chunks * n_slices, heads, n_entries);
@@ -533,7 +589,7 @@ int launch_linear_attention(int heads, int dim, int vdim, const float* decay, co
     const dim3 sgrid((dim * vdim + 127) / 128, heads, n_entries);
     linear_scan_kernel<<<sgrid, 128, 0, s>>>(heads, dim, vdim, decay, state, ent_first, ent_count, ent_seq, ent_pos0, scratch);
     count_launch();
-    linear_chunk_out_kernel<<<grid, kLinThreads, smem, s>>>(heads, dim, vdim, decay, proj, ent_first, ent_count, scratch, o);
+    linear_chunk_out_kernel<<<grid, kLinThreads, smem_out, s>>>(heads, dim, vdim, decay, proj, ent_first, ent_count, scratch, o);
     return done();
   }
   const dim3 grid((vdim + kLinCols - 1) / kLinCols, heads, n_entries);

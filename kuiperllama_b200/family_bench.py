@@ -50,8 +50,9 @@ def kikunex_costs(shape, prompt_len):
     win = min(shape.window, prompt_len)
     pairs = prompt_len * win - win * (win - 1) / 2  # (query, key) pairs inside the window
     H, r, dr = shape.heads, shape.kv_rank, shape.rot_dim
-    # latent attention as the engine computes it: scores and sums over the latent; absorb and expand per token
-    attn_lat = 2 * pairs * H * (2 * r + dr) + 2 * prompt_len * H * r * (shape.dim + shape.vdim)
+    # latent attention in its per-head form: scores over dim + rot_dim, sums over vdim, and the two up-projections of
+    # every token's latent (W_uk c, W_uv c); the absorbed form the engine uses beyond fresh prompts costs more
+    attn_lat = 2 * pairs * H * (shape.dim + dr + shape.vdim) + 2 * prompt_len * H * r * (shape.dim + shape.vdim)
     chunk = 32
     attn_lin = 2 * prompt_len * shape.lin_heads * (chunk / 2 * (shape.lin_dim + shape.lin_vdim) +
                                                     2 * shape.lin_dim * shape.lin_vdim)
