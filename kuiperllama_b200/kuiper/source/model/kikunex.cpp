@@ -65,10 +65,16 @@ base::Status KikunexModel::build_lightning(const json::Value& c, const Safetenso
                                            kllm_seq_linear* a) {
   a->heads = get_int(c, "heads"), a->dim = get_int(c, "dim"), a->vdim = get_int(c, "vdim");
   if (a->heads <= 0 || a->dim <= 0 || a->vdim <= 0) return base::error::ModelParseError(p + ": bad mixer configuration");
-  const auto& decay = c.at("decay").array;
-  if (static_cast<int64_t>(decay.size()) != a->heads) return base::error::ModelParseError(p + ": one decay per head is needed");
+  // one decay per head, or one number for all heads
   std::vector<float> lam;
-  for (const auto& v : decay) lam.push_back(static_cast<float>(v.as_number()));
+  if (c.at("decay").is_array()) {
+    for (const auto& v : c.at("decay").array) lam.push_back(static_cast<float>(v.as_number()));
+  } else {
+    lam.assign(static_cast<size_t>(a->heads), static_cast<float>(c.at("decay").as_number()));
+  }
+  if (static_cast<int64_t>(lam.size()) != a->heads) return base::error::ModelParseError(p + ": one decay per head is needed");
+  for (float v : lam)
+    if (!(v > 0.f) || v > 1.f) return base::error::ModelParseError(p + ": a decay must lie in (0, 1]");
   base::Status st;
   const StTensor *q = need(w, p + "q", &st), *k = need(w, p + "k", &st), *v = need(w, p + "v", &st), *g = need(w, p + "g", &st),
                  *o = need(w, p + "o", &st), *n = need(w, p + "norm", &st);

@@ -337,6 +337,30 @@ def test_bfloat16_products(tmp_path):
     assert rel_err(np.concatenate(logits), ref_logits(cfg, w, t)) < TOL16
 
 
+@pytest.mark.parametrize("dims,window", [((24, 8, 40), 17), ((104, 24, 72), 64), ((136, 56, 128), 150)])
+def test_bfloat16_prompts_on_the_tensor_cores(tmp_path, dims, window):
+    """Prompt steps that start their sequences expand the latents into per-head keys and values and take the tensor-core
+    attention (head sizes that are multiples of 8); single-token steps score against the cached latents.  Both see the
+    same bf16 inputs, so they agree far more tightly than either agrees with float64 -- a key lost at a window's or a
+    tile's edge, or a forgotten sink, would not.  A ragged batch: requests of 1, 70 and 200 tokens."""
+    dim, rot, vdim = dims
+    layers = [(ko.latent_mixer(heads=3, dim=dim, rot_dim=rot, vdim=vdim, kv_rank=48, q_rank=40, window=window), None),
+              (ko.latent_mixer(heads=2, dim=dim, rot_dim=rot, vdim=vdim, kv_rank=32, q_rank=24, window=2 * window + 3),
+               ko.dense_mlp(64))]
+    cfg = ko.make_config(width=64, vocab=90, layers=layers, loop=(0, 1, 2))
+    w = ko.make_weights(cfg, seed=91, sharp=2.0)
+    d = ko.write_model(tmp_path, cfg, w)
+    reqs = {"a": toks(1, 90, 92), "b": toks(70, 90, 93), "c": toks(200, 90, 94)}
+    block = [{"entries": [{"id": k, "tokens": reqs[k], "want": list(range(len(reqs[k])))} for k in "abc"], "end": ["a", "b", "c"]}]
+    steps = block + [st for k in "abc" for st in single(k + "1", reqs[k], end=True)]
+    logits, _ = run_trace(d, steps, dtype="bfloat16", page=16, max_tokens=512)
+    got_block, got_single = logits[0], np.concatenate(logits[1:])
+    ref = np.concatenate([ref_logits(cfg, w, reqs[k]) for k in "abc"])
+    assert rel_err(got_block, ref) < TOL16 and rel_err(got_single, ref) < TOL16
+    err = row_errors(got_block, got_single)
+    assert err.max() < 1.5e-2, f"first bad row {int(np.argmax(err >= 1.5e-2))}"
+
+
 @pytest.mark.parametrize("dtype,tol", [("float32", TOL32), ("bfloat16", TOL16)])
 def test_sizes_that_fit_no_vector(tmp_path, dtype, tol):
     """Width, ranks, inner sizes and head sizes that are not multiples of 8 (nor of 4): no 16-byte row anywhere."""
