@@ -549,7 +549,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
     if (L.mixer_kind == KLLM_SEQ_MIXER_ATTENTION) {
       const kllm_seq_attention& A = L.attn;
       const AttnShape shape{A.heads, A.kv_heads, A.dim, A.vdim, A.scale, A.temp_coef, A.temp_every, A.qk_norm, A.gate,
-                            0, nullptr, 0, 0};
+                            0, nullptr, 0, 0, 0};
       const PagedKV kv{e->k_pool[r], e->v_pool[r], e->table_dev, e->table_stride, e->page, A.kv_heads * A.dim,
                        A.kv_heads * A.vdim};
       const int n_proj = A.heads * A.dim + A.kv_heads * (A.dim + A.vdim) + (A.gate ? A.heads : 0);
@@ -576,7 +576,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       // expanded into per-head keys and values (two products) and the tensor-core attention runs on those rows.  Every
       // other step scores against the cached latents (the absorbed form below).
       const int dqk = A.dim + A.rot_dim;
-      const AttnShape eshape{A.heads, A.heads, dqk, A.vdim, A.scale, 0.f, 0, 0, 1, A.window, A.sink, 0, 0};
+      const AttnShape eshape{A.heads, A.heads, dqk, A.vdim, A.scale, 0.f, 0, 0, 1, A.window, A.sink, 0, 0, 0};
       if (fresh_prompt && attention_mma_usable(dtype, eshape, max_count)) {
         RC(e->lat_c.reserve(Ts * A.kv_rank * es));
         RC(e->lat_kr.reserve(Ts * std::max(1, A.rot_dim) * 4));
@@ -607,10 +607,17 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       RC(launch_latent_absorb(dtype, ls, static_cast<const float*>(e->qf.p), A.w_uk, d_pos, static_cast<float*>(e->qa.p), T, st));
       e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
       // one shared key/value "head": keys [latent | rotated part], values the latent itself
-      const AttnShape shape{A.heads, 1, krow, A.kv_rank, A.scale, 0.f, 0, 0, 1, A.window, A.sink, 1, 1};
+      // steps of single tokens merge the key splits and apply W_uv in one kernel
+      const bool fused_merge = single && T <= 32;
+      const AttnShape shape{A.heads, 1, krow, A.kv_rank, A.scale, 0.f, 0, 0, 1, A.window, A.sink, 1, 1, fused_merge ? 1 : 0};
+      const int lsplits = window_splits(A.window);
       RC(launch_attention(dtype, shape, e->qa.p, gates, kv, n_entries, d_first, d_count, d_eseq, d_pos0, max_count, max_ctx,
-                          window_splits(A.window), static_cast<float*>(e->ws.p), e->ol.p, T, d_seq, d_pos, st));
-      RC(launch_latent_expand(dtype, ls, static_cast<const float*>(e->ol.p), A.w_uv, e->att.p, T, st));
+                          lsplits, static_cast<float*>(e->ws.p), e->ol.p, T, d_seq, d_pos, st));
+      if (fused_merge)
+        RC(launch_latent_merge_expand(dtype, ls, lsplits, static_cast<const float*>(e->ws.p), gates, A.sink, A.w_uv,
+                                      e->att.p, T, st));
+      else
+        RC(launch_latent_expand(dtype, ls, static_cast<const float*>(e->ol.p), A.w_uv, e->att.p, T, st));
       e->mark(KLLM_SEQ_PHASE_ATTENTION);
       RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
       e->mark(KLLM_SEQ_PHASE_OUT_PROJ);

@@ -53,6 +53,7 @@ struct AttnShape {
   const float* sink;  // [heads] or null: exp(sink) is added to the softmax denominator
   int q_f32;        // the queries are fp32 whatever the compute type
   int out_f32;      // the output is written in fp32 whatever the compute type
+  int no_merge;     // leave the splits' partial results in the workspace: the caller merges them (latent_merge_expand)
 };
 
 // ---- seq_kernels.cu -----------------------------------------------------------------------------------------------
@@ -158,6 +159,10 @@ int launch_latent_pack_kv(int dtype, const LatentShape& a, const float* kp, cons
 // q [T, heads, dim + rot_dim] fp32 -> qa [T, heads, kv_rank + rot_dim] fp32: W_uk(head)^T q_plain | rotated q_rot
 int launch_latent_absorb(int dtype, const LatentShape& a, const float* q, const void* w_uk, const int32_t* tok_pos, float* qa,
                          int T, cudaStream_t s);
+// Single-token steps: the merge of the key splits (sink and gate included) and W_uv in one kernel, a CTA per (token, head).
+// ws: the partial results launch_attention left (AttnShape::no_merge) for value size kv_rank.
+int launch_latent_merge_expand(int dtype, const LatentShape& a, int splits, const float* ws, const float* gates,
+                               const float* sink, const void* w_uv, void* out, int T, cudaStream_t s);
 // ol [T, heads, kv_rank] fp32 (weighted sums of latents) -> out [T, heads * vdim] compute type: W_uv(head) ol
 int launch_latent_expand(int dtype, const LatentShape& a, const float* ol, const void* w_uv, void* out, int T, cudaStream_t s);
 

@@ -1007,7 +1007,7 @@ int launch_attention(int dtype, const AttnShape& a, const void* q, const float* 
   }
 #undef KLLM_ATTN_C
   }
-  if (rc) return rc;
+  if (rc || a.no_merge) return rc;
   KLLM_SEQ_DISPATCH(dtype, (attention_merge_kernel<AT><<<T * a.heads, 64, 0, s>>>(a.heads, a.vdim, splits, ws,
                                                                                  a.gate ? gates : nullptr, a.sink, a.out_f32,
                                                                                  out)));

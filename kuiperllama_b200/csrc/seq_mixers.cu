@@ -111,7 +111,8 @@ __global__ void latent_absorb_kernel(LatentShape a, const float* __restrict__ q,
     qs[i] = q[(static_cast<size_t>(t0 + i / dq) * a.heads + h) * dq + i % dq];
   __syncthreads();
   const AT* w = w_uk + static_cast<size_t>(h) * a.dim * a.kv_rank;
-  for (int r = threadIdx.x; r < a.kv_rank; r += blockDim.x) {
+  // blockIdx.z: a slice of the latent coordinates, so that a step of few tokens still spreads over many SMs
+  for (int r = blockIdx.z * blockDim.x + threadIdx.x; r < a.kv_rank; r += gridDim.z * blockDim.x) {
     float acc[kAbsTokens];
 #pragma unroll
     for (int j = 0; j < kAbsTokens; ++j) acc[j] = 0.f;
@@ -124,6 +125,7 @@ __global__ void latent_absorb_kernel(LatentShape a, const float* __restrict__ q,
     for (int j = 0; j < kAbsTokens; ++j)
       if (j < n) qa[(static_cast<size_t>(t0 + j) * a.heads + h) * dl + r] = acc[j];
   }
+  if (blockIdx.z != 0) return;
   for (int i = threadIdx.x; i < n * a.rot_dim; i += blockDim.x) {
     const int j = i / a.rot_dim, c = i % a.rot_dim;
     qa[(static_cast<size_t>(t0 + j) * a.heads + h) * dl + a.kv_rank + c] =
@@ -190,6 +192,45 @@ __global__ void latent_expand_kernel(LatentShape a, const float* __restrict__ ol
       const float v = warp_sum(acc[j]);
       if (lane == 0 && j < n) out[(static_cast<size_t>(t0 + j) * a.heads + h) * a.vdim + f] = from_f<AT>(v);
     }
+  }
+}
+
+// The same for steps of single tokens, fused with the merge of the key splits: a CTA per (token, head) joins the splits'
+// (max, sum, unnormalised latent sums), adds the sink to the denominator, applies the gate, and multiplies by the head's
+// block of W_uv -- the merged latent sum never leaves shared memory.
+template <typename AT>
+__global__ void latent_merge_expand_kernel(LatentShape a, int splits, const float* __restrict__ ws,
+                                           const float* __restrict__ gates, const float* __restrict__ sink,
+                                           const AT* __restrict__ w_uv, AT* __restrict__ out) {
+  extern __shared__ float ls[];  // [kv_rank]
+  const size_t th = blockIdx.x;  // t * heads + h
+  const int h = static_cast<int>(th % a.heads);
+  const int pstride = a.kv_rank + 2;
+  const float* p = ws + th * splits * pstride;
+  float M = sink ? sink[h] : -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, p[s * pstride]);
+  float L = sink ? expf(sink[h] - M) : 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float m = p[s * pstride];
+    if (m > -INFINITY) L += p[s * pstride + 1] * expf(m - M);
+  }
+  const float g = (gates ? gates[th] : 1.0f) / L;
+  for (int d = threadIdx.x; d < a.kv_rank; d += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float m = p[s * pstride];
+      if (m > -INFINITY) o += p[s * pstride + 2 + d] * expf(m - M);
+    }
+    ls[d] = o * g;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int f = warp; f < a.vdim; f += nw) {
+    const AT* w = w_uv + (static_cast<size_t>(h) * a.vdim + f) * a.kv_rank;
+    float acc = 0.f;
+    for (int r = lane; r < a.kv_rank; r += 32) acc = fmaf(ls[r], to_f(w[r]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) out[th * a.vdim + f] = from_f<AT>(acc);
   }
 }
 
@@ -535,10 +576,19 @@ int launch_latent_absorb(int dtype, const LatentShape& a, const float* q, const 
                          int T, cudaStream_t s) {
   const size_t smem = static_cast<size_t>(kAbsTokens) * (a.dim + a.rot_dim) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
-  const dim3 grid((T + kAbsTokens - 1) / kAbsTokens, a.heads);
-  const int threads = a.kv_rank <= 64 ? 64 : (a.kv_rank <= 128 ? 128 : 256);
+  // few tokens: 64 latent coordinates per CTA; many tokens: the whole latent (the queries are staged once per CTA)
+  const int threads = T <= kAbsTokens ? 64 : (a.kv_rank <= 64 ? 64 : (a.kv_rank <= 128 ? 128 : 256));
+  const dim3 grid((T + kAbsTokens - 1) / kAbsTokens, a.heads, (a.kv_rank + threads - 1) / threads);
   KLLM_SEQ_DISPATCH(dtype, (latent_absorb_kernel<AT><<<grid, threads, smem, s>>>(a, q, static_cast<const AT*>(w_uk), tok_pos,
                                                                                 qa, T)));
+  return done();
+}
+
+int launch_latent_merge_expand(int dtype, const LatentShape& a, int splits, const float* ws, const float* gates,
+                               const float* sink, const void* w_uv, void* out, int T, cudaStream_t s) {
+  const size_t smem = static_cast<size_t>(a.kv_rank) * sizeof(float);
+  KLLM_SEQ_DISPATCH(dtype, (latent_merge_expand_kernel<AT><<<T * a.heads, 256, smem, s>>>(
+                               a, splits, ws, gates, sink, static_cast<const AT*>(w_uv), static_cast<AT*>(out))));
   return done();
 }
 
