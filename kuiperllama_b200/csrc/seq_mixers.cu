@@ -116,6 +116,7 @@ __global__ void latent_absorb_kernel(LatentShape a, const float* __restrict__ q,
     float acc[kAbsTokens];
 #pragma unroll
     for (int j = 0; j < kAbsTokens; ++j) acc[j] = 0.f;
+#pragma unroll 8
     for (int d = 0; d < a.dim; ++d) {
       const float wv = to_f(w[static_cast<size_t>(d) * a.kv_rank + r]);
 #pragma unroll
@@ -241,6 +242,25 @@ __global__ void latent_merge_expand_kernel(LatentShape a, int splits, const floa
 //     o_i = l^(i+1) S^T q_i + sum_(j <= i) l^(i-j) (q_i . k_j) v_j
 //     S  <- l^n S + sum_j l^(n-1-j) k_j v_j^T
 // Only non-negative powers of l appear.  Everything is fp32; silu is applied to q, k, v as they are loaded.
+// Fill shared memory from global memory with U loads of a thread in flight before the first is used: the tiles of these
+// kernels are small and each CTA waits for them once, so the loop is bound by load latency, not by bandwidth.
+template <int U, typename Load, typename Store>
+__device__ __forceinline__ void staged_fill(int total, Load load, Store store) {
+  for (int i0 = threadIdx.x; i0 < total; i0 += blockDim.x * U) {
+    float v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * blockDim.x;
+      v[u] = i < total ? load(i) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * blockDim.x;
+      if (i < total) store(i, v[u]);
+    }
+  }
+}
+
 constexpr int kLinChunk = 32;
 constexpr int kLinCols = 32;
 constexpr int kLinThreads = 128;
@@ -268,25 +288,22 @@ linear_attention_kernel(int heads, int dim, int vdim, const float* __restrict__ 
   if (tid <= kLinChunk) pw[tid] = tid == 0 ? 1.0f : expf(llog * static_cast<float>(tid));
   float* sg = state + ((static_cast<size_t>(seq) * heads + h) * dim) * vdim;
   const bool fresh = ent_pos0[e] == 0;
-  for (int i = tid; i < dim * kLinCols; i += kLinThreads) {
-    const int d = i / kLinCols, c = i % kLinCols;
-    Ss[i] = (!fresh && c < cols) ? sg[static_cast<size_t>(d) * vdim + c0 + c] : 0.f;
-  }
+  staged_fill<8>(dim * kLinCols,
+                 [&](int i) { return (!fresh && i % kLinCols < cols) ? sg[static_cast<size_t>(i / kLinCols) * vdim + c0 + i % kLinCols] : 0.f; },
+                 [&](int i, float v) { Ss[i] = v; });
   const int qn = heads * dim, vn = heads * vdim;
   const int stride = 2 * qn + 2 * vn;
   for (int base = 0; base < count; base += kLinChunk) {
     const int n = min(kLinChunk, count - base);
     __syncthreads();  // the previous chunk's tiles are no longer read; Ss / pw are written
-    for (int i = tid; i < n * dim; i += kLinThreads) {
-      const int j = i / dim, d = i % dim;
-      const float* row = proj + static_cast<size_t>(first + base + j) * stride;
-      Qs[j * dp + d] = siluf(row[h * dim + d]);
-      Ks[j * dp + d] = siluf(row[qn + h * dim + d]);
-    }
-    for (int i = tid; i < n * kLinCols; i += kLinThreads) {
-      const int j = i / kLinCols, c = i % kLinCols;
-      Vs[i] = c < cols ? siluf(proj[static_cast<size_t>(first + base + j) * stride + 2 * qn + h * vdim + c0 + c]) : 0.f;
-    }
+    const float* rows = proj + static_cast<size_t>(first + base) * stride;
+    staged_fill<8>(n * dim, [&](int i) { return rows[static_cast<size_t>(i / dim) * stride + h * dim + i % dim]; },
+                   [&](int i, float v) { Qs[(i / dim) * dp + i % dim] = siluf(v); });
+    staged_fill<8>(n * dim, [&](int i) { return rows[static_cast<size_t>(i / dim) * stride + qn + h * dim + i % dim]; },
+                   [&](int i, float v) { Ks[(i / dim) * dp + i % dim] = siluf(v); });
+    staged_fill<8>(n * kLinCols,
+                   [&](int i) { return i % kLinCols < cols ? rows[static_cast<size_t>(i / kLinCols) * stride + 2 * qn + h * vdim + c0 + i % kLinCols] : 0.f; },
+                   [&](int i, float v) { Vs[i] = siluf(v); });
     __syncthreads();
     for (int i = tid; i < n * n; i += kLinThreads) {  // decayed scores inside the chunk
       const int r = i / n, j = i % n;
@@ -347,15 +364,16 @@ linear_chunk_sums_kernel(int heads, int dim, int vdim, const float* __restrict__
   const int tid = threadIdx.x;
   const float llog = logf(decay[h]);
   const int qn = heads * dim, vn = heads * vdim, stride = 2 * qn + 2 * vn;
-  for (int i = tid; i < n * dim; i += kLinThreads) {
-    const int j = i / dim, d = i % dim;
-    const float w = n - 1 - j == 0 ? 1.0f : expf(llog * static_cast<float>(n - 1 - j));
-    Ks[j * dp + d] = siluf(proj[static_cast<size_t>(first + base + j) * stride + qn + h * dim + d]) * w;
-  }
-  for (int i = tid; i < n * kLinCols; i += kLinThreads) {
-    const int j = i / kLinCols, c = i % kLinCols;
-    Vs[i] = c < cols ? siluf(proj[static_cast<size_t>(first + base + j) * stride + 2 * qn + h * vdim + c0 + c]) : 0.f;
-  }
+  const float* rows = proj + static_cast<size_t>(first + base) * stride;
+  staged_fill<8>(n * dim, [&](int i) { return rows[static_cast<size_t>(i / dim) * stride + qn + h * dim + i % dim]; },
+                 [&](int i, float v) {
+                   const int j = i / dim;
+                   const float w = n - 1 - j == 0 ? 1.0f : expf(llog * static_cast<float>(n - 1 - j));
+                   Ks[j * dp + i % dim] = siluf(v) * w;
+                 });
+  staged_fill<8>(n * kLinCols,
+                 [&](int i) { return i % kLinCols < cols ? rows[static_cast<size_t>(i / kLinCols) * stride + 2 * qn + h * vdim + c0 + i % kLinCols] : 0.f; },
+                 [&](int i, float v) { Vs[i] = siluf(v); });
   __syncthreads();
   float* out = sums + (chunk_slot(first, base, e) * heads + h) * dim * vdim;
   for (int i = tid; i < dim * kLinCols; i += kLinThreads) {
@@ -427,26 +445,21 @@ linear_chunk_out_kernel(int heads, int dim, int vdim, const float* __restrict__ 
   const float llog = logf(decay[h]);
   if (tid <= kLinChunk) pw[tid] = tid == 0 ? 1.0f : expf(llog * static_cast<float>(tid));
   const float* sb = sums + (chunk_slot(first, base, e) * heads + h) * dim * vdim;
-  for (int i = tid; i < d4 * kLinCols; i += kLinThreads) {
-    const int d = i / kLinCols, c = i % kLinCols;
-    Ss[i] = (d < dim && c < cols) ? sb[static_cast<size_t>(d) * vdim + c0 + c] : 0.f;
-  }
+  staged_fill<8>(d4 * kLinCols,
+                 [&](int i) { return (i / kLinCols < dim && i % kLinCols < cols) ? sb[static_cast<size_t>(i / kLinCols) * vdim + c0 + i % kLinCols] : 0.f; },
+                 [&](int i, float v) { Ss[i] = v; });
   const int qn = heads * dim, vn = heads * vdim, stride = 2 * qn + 2 * vn;
-  for (int i = tid; i < kLinChunk * d4; i += kLinThreads) {
-    const int j = i / d4, d = i % d4;
-    float qv = 0.f, kv = 0.f;
-    if (j < n && d < dim) {
-      const float* row = proj + static_cast<size_t>(first + base + j) * stride;
-      qv = siluf(row[h * dim + d]);
-      kv = siluf(row[qn + h * dim + d]);
-    }
-    Qs[j * dp + d] = qv;
-    Ks[j * dp + d] = kv;
-  }
-  for (int i = tid; i < kLinChunk * kLinCols; i += kLinThreads) {
-    const int j = i / kLinCols, c = i % kLinCols;
-    Vs[i] = (j < n && c < cols) ? siluf(proj[static_cast<size_t>(first + base + j) * stride + 2 * qn + h * vdim + c0 + c]) : 0.f;
-  }
+  const float* rows = proj + static_cast<size_t>(first + base) * stride;
+  // silu(0) = 0: rows and coordinates past the chunk load as zeros
+  staged_fill<8>(kLinChunk * d4,
+                 [&](int i) { return (i / d4 < n && i % d4 < dim) ? rows[static_cast<size_t>(i / d4) * stride + h * dim + i % d4] : 0.f; },
+                 [&](int i, float v) { Qs[(i / d4) * dp + i % d4] = siluf(v); });
+  staged_fill<8>(kLinChunk * d4,
+                 [&](int i) { return (i / d4 < n && i % d4 < dim) ? rows[static_cast<size_t>(i / d4) * stride + qn + h * dim + i % d4] : 0.f; },
+                 [&](int i, float v) { Ks[(i / d4) * dp + i % d4] = siluf(v); });
+  staged_fill<8>(kLinChunk * kLinCols,
+                 [&](int i) { return (i / kLinCols < n && i % kLinCols < cols) ? rows[static_cast<size_t>(i / kLinCols) * stride + 2 * qn + h * vdim + c0 + i % kLinCols] : 0.f; },
+                 [&](int i, float v) { Vs[i] = siluf(v); });
   __syncthreads();
   constexpr int R = kLinChunk / 4;  // rows per thread
   {  // decayed scores inside the chunk: lane = key j, rows warp + 4 k
