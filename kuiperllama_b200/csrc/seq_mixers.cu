@@ -346,11 +346,15 @@ linear_attention_kernel(int heads, int dim, int vdim, const float* __restrict__ 
 // Chunk j of entry e lives in slot (first_e + j * chunk) / chunk + e of the scratch buffer [slots][heads][dim][vdim].
 __device__ __forceinline__ size_t chunk_slot(int first, int base, int e) { return static_cast<size_t>((first + base) / kLinChunk + e); }
 
+__host__ __device__ inline int lin_dp(int dim) { return ((dim + 3) & ~3) + 4; }  // row stride of Qs / Ks: 16-byte rows, odd in 16-byte units for dim % 8 == 0
+
+// A thread keeps 8 consecutive key coordinates of one value column: two 16-byte broadcast loads and one column load
+// feed 8 multiply-adds.
 __global__ void __launch_bounds__(kLinThreads)
 linear_chunk_sums_kernel(int heads, int dim, int vdim, const float* __restrict__ decay, const float* __restrict__ proj,
                          const int32_t* __restrict__ ent_first, const int32_t* __restrict__ ent_count,
                          float* __restrict__ sums) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   const int e = blockIdx.z, h = blockIdx.y;
   const int n_slices = (vdim + kLinCols - 1) / kLinCols;
   const int chunk = blockIdx.x / n_slices, c0 = (blockIdx.x % n_slices) * kLinCols;
@@ -358,29 +362,39 @@ linear_chunk_sums_kernel(int heads, int dim, int vdim, const float* __restrict__
   if (base >= count) return;
   const int n = min(kLinChunk, count - base);
   const int cols = min(kLinCols, vdim - c0);
-  const int dp = dim + 1;
-  float* Ks = sm;                       // [chunk][dp], already times l^(n-1-j)
+  const int d8 = (dim + 7) & ~7, dp = lin_dp(dim);
+  float* Ks = sm;                       // [chunk][dp], already times l^(n-1-j); zeros from dim to d8
   float* Vs = Ks + kLinChunk * dp;      // [chunk][kLinCols]
-  const int tid = threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float llog = logf(decay[h]);
   const int qn = heads * dim, vn = heads * vdim, stride = 2 * qn + 2 * vn;
   const float* rows = proj + static_cast<size_t>(first + base) * stride;
-  staged_fill<8>(n * dim, [&](int i) { return rows[static_cast<size_t>(i / dim) * stride + qn + h * dim + i % dim]; },
+  staged_fill<8>(n * d8,
+                 [&](int i) { return i % d8 < dim ? rows[static_cast<size_t>(i / d8) * stride + qn + h * dim + i % d8] : 0.f; },
                  [&](int i, float v) {
-                   const int j = i / dim;
+                   const int j = i / d8;
                    const float w = n - 1 - j == 0 ? 1.0f : expf(llog * static_cast<float>(n - 1 - j));
-                   Ks[j * dp + i % dim] = siluf(v) * w;
+                   Ks[j * dp + i % d8] = siluf(v) * w;
                  });
   staged_fill<8>(n * kLinCols,
                  [&](int i) { return i % kLinCols < cols ? rows[static_cast<size_t>(i / kLinCols) * stride + 2 * qn + h * vdim + c0 + i % kLinCols] : 0.f; },
                  [&](int i, float v) { Vs[i] = siluf(v); });
   __syncthreads();
   float* out = sums + (chunk_slot(first, base, e) * heads + h) * dim * vdim;
-  for (int i = tid; i < dim * kLinCols; i += kLinThreads) {
-    const int d = i / kLinCols, c = i % kLinCols;
-    float acc = 0.f;
-    for (int j = 0; j < n; ++j) acc = fmaf(Ks[j * dp + d], Vs[j * kLinCols + c], acc);
-    if (c < cols) out[static_cast<size_t>(d) * vdim + c0 + c] = acc;
+  for (int d0 = warp * 8; d0 < d8; d0 += (kLinThreads / 32) * 8) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int j = 0; j < n; ++j) {
+      const float v = Vs[j * kLinCols + lane];
+      const float4 a = *reinterpret_cast<const float4*>(Ks + j * dp + d0);
+      const float4 b = *reinterpret_cast<const float4*>(Ks + j * dp + d0 + 4);
+      acc[0] = fmaf(a.x, v, acc[0]), acc[1] = fmaf(a.y, v, acc[1]), acc[2] = fmaf(a.z, v, acc[2]), acc[3] = fmaf(a.w, v, acc[3]);
+      acc[4] = fmaf(b.x, v, acc[4]), acc[5] = fmaf(b.y, v, acc[5]), acc[6] = fmaf(b.z, v, acc[6]), acc[7] = fmaf(b.w, v, acc[7]);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (d0 + k < dim && lane < cols) out[static_cast<size_t>(d0 + k) * vdim + c0 + lane] = acc[k];
   }
 }
 
@@ -419,7 +433,6 @@ __global__ void linear_scan_kernel(int heads, int dim, int vdim, const float* __
 
 // Each thread keeps 8 rows (warp + 4 k) of one column: a 16-byte broadcast load brings four coordinates of a row, so the
 // inner loops issue 12 shared-memory loads for 32 multiply-adds.  Rows and coordinates past the chunk are zero-filled.
-__host__ __device__ inline int lin_dp(int dim) { return ((dim + 3) & ~3) + 4; }  // row stride of Qs / Ks: 16-byte rows, odd in 16-byte units for dim % 8 == 0
 constexpr int kLinAs = kLinChunk + 4;
 
 __global__ void __launch_bounds__(kLinThreads)
@@ -646,7 +659,7 @@ int launch_linear_attention(int heads, int dim, int vdim, const float* decay, co
     }
     const int n_slices = (vdim + kLinCols - 1) / kLinCols, chunks = (max_count + kLinChunk - 1) / kLinChunk;
     const dim3 grid(chunks * n_slices, heads, n_entries);
-    const size_t smem_sums = (static_cast<size_t>(kLinChunk) * (dim + 1) + kLinChunk * kLinCols) * sizeof(float);
+    const size_t smem_sums = (static_cast<size_t>(kLinChunk) * lin_dp(dim) + kLinChunk * kLinCols) * sizeof(float);
     linear_chunk_sums_kernel<<<grid, kLinThreads, smem_sums, s>>>(heads, dim, vdim, decay, proj, ent_first, ent_count, scratch);
     count_launch();
     const dim3 sgrid((dim * vdim + 127) / 128, heads, n_entries);

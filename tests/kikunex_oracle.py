@@ -221,7 +221,7 @@ def moe_mlp(experts=6, top=2, ff=16, groups=(3, 2), scale=1.5):
     return {"kind": "moe", "expert": {"ff": ff}, "router": r}
 
 
-def make_config(width=48, vocab=61, layers=(), loop=None, eps=1e-5, logit_scale=0.7):
+def make_config(width=48, vocab=61, layers=(), loop=None, eps=3e-6, logit_scale=0.7):
     """layers: [(mixer dict, mlp dict or None)]."""
     cfg = {"architecture": "Kikunex", "vocab": vocab, "width": width, "norm": {"eps": eps}, "logit_scale": logit_scale,
            "layers": [dict(m, mlp=f) for m, f in layers]}
