@@ -7,21 +7,33 @@
 // sequence takes pages as it grows (lowest free number first, so freed pages are the next to be used again) and
 // returns them at close.  The table rows of the step's sequences are copied to the device before the kernels run.
 //
+// State.  Beside the pages, every layer run owns per-slot recurrent state in fp32: the last mixer input of a layer with a
+// token shift, and the matrix state of linear attention.  A sequence of length 0 reads zeros instead of its slot's
+// memory, so slots are reused without clearing.  A run of attention through a latent keeps one row per token in its pool
+// (latent | rotated key part); its values are the head of that row.
+//
 // Step.  Host work: validate, take pages, fill the per-token / per-entry index arrays in pinned memory, one
 // host->device copy.  Device work, per layer run:
-//     resid_norm   (x += run vector)  h = LN_pre(x)
-//     gemm         q | k | v | gate rows in one product
-//     qk_prepare   RMS norms, query temperature, scatter of k / v into the pages, sigmoid of the gates
-//     attention    causal, paged, keys split over CTAs; merge applies the gate
+//     resid_norm   what comes ahead of the mixer: (x += embedding output) (x += run vector)  h = N_pre(x), and the token
+//                  shift -- inside this kernel when every entry is one token, else by token_shift on the fp32 rows
+//     mixer        attention:  gemm (q | k | v | gate rows), qk_prepare (RMS norms, temperature, scatter of k / v into the
+//                              pages, gates), attention (causal, paged, keys split over CTAs; merge applies the gate)
+//                  latent:     gemm (query and key/value down-projections, gate rows), latent_prepare (norms, rotation,
+//                              cache row, gates), gemm (query up-projection); then either the absorbed form -- absorb,
+//                              paged attention over the latents with window and sink, merge, value expansion -- or, for
+//                              bf16 prompts that start their sequences, per-head keys and values of the step's own
+//                              latents (two products) and the tensor-core attention
+//                  linear:     gemm (q | k | v | gate rows), the decayed-state recurrence (one kernel for short entries,
+//                              chunk sums / scan / chunk outputs for long ones), output norm and gate
 //     gemm         output projection
-//     resid_norm   x += LN_post(y);  h = LN_pre_ff(x);  router on h: fp32 logits, softmax, top-k, weights,
-//                  shared-expert gate (same kernel: the row is still in shared memory)
-//     experts      few tokens: pair kernels (weights streamed once per chosen expert; the shared expert rides along
-//                  as one more pair per token, so the three `shared` kernels below are not launched)
-//                  many tokens: pairs sorted by expert, two grouped products (SiLU-gate epilogue in the first)
-//     shared       gemm gate|up, silu_mul, gemm down
-//     resid_norm   x += LN_post_ff(routed + g_shared * shared)   [+ the next run's vector and pre-norm, fused]
-// then the final norm on the wanted rows only, the classifier product, argmax, and one device->host copy.
+//     resid_norm   x += N_post(y);  h = N_pre_ff(x);  router on h (softmax or sigmoid with groups): same kernel, the row
+//                  is still in shared memory
+//     feed-forward dense: gemm, activation, gemm
+//                  experts, few tokens: pair kernels (weights streamed once per chosen expert; a shared expert rides
+//                  along as one more pair per token); many tokens: pairs sorted by expert, two grouped products (SiLU-gate
+//                  or squared-ReLU epilogue in the first); shared expert: gemm gate|up, silu_mul, gemm down
+//     resid_norm   x += N_post_ff(ff output)   [+ what comes ahead of the next run's mixer, fused]
+// then the final norm on the wanted rows only, the classifier product, the logit scale, argmax, and one device->host copy.
 #include <cuda_runtime.h>
 
 #include <algorithm>

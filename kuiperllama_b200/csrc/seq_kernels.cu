@@ -1,7 +1,9 @@
-// Kernels of the sequence-batch engine other than the matrix products: embedding rows, the fused residual /
-// layer-norm step, query-key preparation with the scatter into the paged cache, causal paged attention (prompt tiles
-// and single decode rows through the same kernel, keys split over CTAs), the softmax router with top-k selection, and
-// the routed experts one (token, expert) pair at a time for steps of a few tokens.
+// Kernels of the sequence-batch engine other than the matrix products: embedding rows (with their norm), the fused
+// residual / norm step (layer norm or RMS norm; token shift for single-token steps; router), the token shift over longer
+// entries, query-key preparation with the scatter into the paged cache, causal paged attention (prompt tiles and single
+// decode rows through the same kernel, keys split over CTAs, optional window, sink and fp32 queries), the softmax and the
+// grouped sigmoid router with top-k selection, and the routed experts one (token, expert) pair at a time for steps of a
+// few tokens.  The mixers with other kinds of memory (latents, recurrent state) are in seq_mixers.cu.
 //
 // Every kernel is a template on the compute type AT (float or __nv_bfloat16): what the matrix products read and
 // write.  Norms, scores, softmax weights, router and residual are fp32 in both instantiations.

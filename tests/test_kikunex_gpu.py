@@ -396,6 +396,76 @@ def test_larger_shapes_take_the_block_paths(tmp_path):
             assert np.median(err) < tol / 2 and (err > tol).mean() <= 0.1 and err.max() < 4 * tol, np.sort(err)[-5:]
 
 
+def random_design(seed):
+    """A model of the size a checkpoint of this family might have: every size and constant drawn, layer order too."""
+    rng = np.random.default_rng(seed)
+    pick = lambda *xs: xs[int(rng.integers(len(xs)))]  # noqa: E731
+    layers = []
+    for _ in range(int(rng.integers(4, 8))):
+        if rng.random() < 0.5:
+            m = ko.latent_mixer(heads=pick(2, 4, 6, 8), dim=pick(16, 24, 32, 48), rot_dim=pick(8, 16, 32), vdim=pick(16, 40, 48, 64),
+                                kv_rank=pick(32, 48, 80, 128), q_rank=pick(24, 64, 112), window=int(rng.integers(5, 130)),
+                                base=float(pick(1e4, 1e5, 1e6)))
+        else:
+            H = pick(2, 3, 4, 6)
+            m = ko.lightning_mixer(heads=H, dim=pick(16, 32, 48), vdim=pick(16, 32, 64),
+                                   decay=[float(x) for x in np.exp(-1.0 / rng.uniform(1.5, 900.0, H))])
+        r = rng.random()
+        if r < 0.25:
+            f = None
+        elif r < 0.5:
+            f = ko.dense_mlp(pick(96, 160, 320))
+        else:
+            count = pick(2, 3, 4)
+            f = ko.moe_mlp(count * pick(2, 3, 4), pick(1, 2, 3, 4), pick(32, 48, 96), (count, int(rng.integers(1, count + 1))),
+                           scale=float(rng.uniform(0.5, 3.0)))
+            f["router"]["top"] = min(f["router"]["top"], f["router"]["groups"]["keep"] * f["router"]["experts"] // count)
+        layers.append((m, f))
+    n = len(layers)
+    start = int(rng.integers(0, n))
+    loop = (start, int(rng.integers(start + 1, n + 1)), int(rng.integers(1, 4))) if rng.random() < 0.8 else None
+    cfg = ko.make_config(width=pick(96, 160, 224), vocab=int(rng.integers(200, 500)), layers=layers, loop=loop,
+                         eps=float(pick(1e-6, 1e-5, 1e-4)), logit_scale=float(rng.uniform(0.3, 1.5)))
+    return cfg, ko.make_weights(cfg, seed=1000 + seed, sharp=1.5)
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5])
+def test_random_designs(tmp_path, seed):
+    """Whole prompts of unequal requests in one batch, then decoded together until the shorter ones end, in both
+    compute types."""
+    cfg, w = random_design(seed)
+    d = ko.write_model(tmp_path, cfg, w)
+    V = cfg["vocab"]
+    reqs = {"a": toks(150, V, seed), "b": toks(37, V, seed + 10), "c": toks(1, V, seed + 20)}
+    tails = {"a": toks(40, V, seed + 30), "b": toks(25, V, seed + 40), "c": toks(9, V, seed + 50)}
+    steps = [{"entries": [{"id": k, "tokens": reqs[k], "want": list(range(len(reqs[k])))} for k in "abc"]}]
+    for j in range(40):
+        live = [k for k in "abc" if j < len(tails[k])]
+        steps.append({"entries": [{"id": k, "tokens": [tails[k][j]], "want": [0]} for k in live],
+                      "end": [k for k in live if j == len(tails[k]) - 1]})
+    refs = {k: ref_logits(cfg, w, reqs[k] + tails[k]) for k in "abc"}
+    for dtype in ("float32", "bfloat16"):
+        logits, _ = run_trace(d, steps, dtype=dtype, max_tokens=400)
+        loose = []
+        for k in "abc":
+            rows, at = [], 0
+            for kk in "abc":
+                if kk == k:
+                    rows.append(logits[0][at:at + len(reqs[kk])])
+                at += len(reqs[kk])
+            for j in range(len(tails[k])):
+                live = [kk for kk in "abc" if j < len(tails[kk])]
+                rows.append(logits[1 + j][live.index(k)][None])
+            got = np.concatenate(rows)
+            if dtype == "float32":
+                assert_rows(got, refs[k])
+            else:
+                loose.append(row_errors(got, refs[k]))
+        if loose:  # a close routing choice flips under bf16 rounding now and then: it touches that row and, fading, the next
+            err = np.concatenate(loose)
+            assert np.median(err) < TOL16 / 2 and (err > TOL16).mean() <= 0.05, np.sort(err)[-5:]
+
+
 def test_greedy_generation_through_the_scheduler(base):
     from kuiperllama_b200 import build
     cfg, w, d = base
