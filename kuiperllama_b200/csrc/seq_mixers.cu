@@ -431,11 +431,12 @@ __global__ void linear_scan_kernel(int heads, int dim, int vdim, const float* __
   *sg = s;
 }
 
-// Each thread keeps 8 rows (warp + 4 k) of one column: a 16-byte broadcast load brings four coordinates of a row, so the
-// inner loops issue 12 shared-memory loads for 32 multiply-adds.  Rows and coordinates past the chunk are zero-filled.
+// Each thread keeps kLinChunk / warps rows (warp + warps * k) of one column: a 16-byte broadcast load brings four coordinates
+// of a row.  Eight warps per CTA: the shared-memory tiles allow few CTAs per SM, so the warps have to come from the CTA.  Rows and coordinates past the chunk are zero-filled.
 constexpr int kLinAs = kLinChunk + 4;
 
-__global__ void __launch_bounds__(kLinThreads)
+constexpr int kLinOutThreads = 256, kLinOutWarps = kLinOutThreads / 32;
+__global__ void __launch_bounds__(kLinOutThreads)
 linear_chunk_out_kernel(int heads, int dim, int vdim, const float* __restrict__ decay, const float* __restrict__ proj,
                         const int32_t* __restrict__ ent_first, const int32_t* __restrict__ ent_count,
                         const float* __restrict__ sums, float* __restrict__ o) {
@@ -474,8 +475,8 @@ linear_chunk_out_kernel(int heads, int dim, int vdim, const float* __restrict__ 
                  [&](int i) { return (i / kLinCols < n && i % kLinCols < cols) ? rows[static_cast<size_t>(i / kLinCols) * stride + 2 * qn + h * vdim + c0 + i % kLinCols] : 0.f; },
                  [&](int i, float v) { Vs[i] = siluf(v); });
   __syncthreads();
-  constexpr int R = kLinChunk / 4;  // rows per thread
-  {  // decayed scores inside the chunk: lane = key j, rows warp + 4 k
+  constexpr int R = kLinChunk / kLinOutWarps;  // rows per thread
+  {  // decayed scores inside the chunk: lane = key j, rows warp + 8 k
     float acc[R];
 #pragma unroll
     for (int k = 0; k < R; ++k) acc[k] = 0.f;
@@ -483,18 +484,18 @@ linear_chunk_out_kernel(int heads, int dim, int vdim, const float* __restrict__ 
       const float4 kv = *reinterpret_cast<const float4*>(Ks + lane * dp + d);
 #pragma unroll
       for (int k = 0; k < R; ++k) {
-        const float4 qv = *reinterpret_cast<const float4*>(Qs + (warp + 4 * k) * dp + d);
+        const float4 qv = *reinterpret_cast<const float4*>(Qs + (warp + kLinOutWarps * k) * dp + d);
         acc[k] = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, fmaf(qv.w, kv.w, acc[k]))));
       }
     }
 #pragma unroll
     for (int k = 0; k < R; ++k) {
-      const int r = warp + 4 * k;
+      const int r = warp + kLinOutWarps * k;
       As[r * kLinAs + lane] = (lane <= r && r < n) ? acc[k] * pw[r - lane] : 0.f;
     }
   }
   __syncthreads();
-  {  // outputs: lane = column, rows warp + 4 k
+  {  // outputs: lane = column, rows warp + 8 k
     float acc[R];
 #pragma unroll
     for (int k = 0; k < R; ++k) acc[k] = 0.f;
@@ -503,24 +504,24 @@ linear_chunk_out_kernel(int heads, int dim, int vdim, const float* __restrict__ 
                   s3 = Ss[(d + 3) * kLinCols + lane];
 #pragma unroll
       for (int k = 0; k < R; ++k) {
-        const float4 qv = *reinterpret_cast<const float4*>(Qs + (warp + 4 * k) * dp + d);
+        const float4 qv = *reinterpret_cast<const float4*>(Qs + (warp + kLinOutWarps * k) * dp + d);
         acc[k] = fmaf(qv.x, s0, fmaf(qv.y, s1, fmaf(qv.z, s2, fmaf(qv.w, s3, acc[k]))));
       }
     }
 #pragma unroll
-    for (int k = 0; k < R; ++k) acc[k] *= pw[min(warp + 4 * k + 1, kLinChunk)];
+    for (int k = 0; k < R; ++k) acc[k] *= pw[min(warp + kLinOutWarps * k + 1, kLinChunk)];
     for (int j = 0; j < kLinChunk; j += 4) {
       const float v0 = Vs[j * kLinCols + lane], v1 = Vs[(j + 1) * kLinCols + lane], v2 = Vs[(j + 2) * kLinCols + lane],
                   v3 = Vs[(j + 3) * kLinCols + lane];
 #pragma unroll
       for (int k = 0; k < R; ++k) {
-        const float4 av = *reinterpret_cast<const float4*>(As + (warp + 4 * k) * kLinAs + j);
+        const float4 av = *reinterpret_cast<const float4*>(As + (warp + kLinOutWarps * k) * kLinAs + j);
         acc[k] = fmaf(av.x, v0, fmaf(av.y, v1, fmaf(av.z, v2, fmaf(av.w, v3, acc[k]))));
       }
     }
 #pragma unroll
     for (int k = 0; k < R; ++k) {
-      const int r = warp + 4 * k;
+      const int r = warp + kLinOutWarps * k;
       if (r < n && lane < cols) o[static_cast<size_t>(first + base + r) * vn + h * vdim + c0 + lane] = acc[k];
     }
   }
@@ -665,7 +666,7 @@ int launch_linear_attention(int heads, int dim, int vdim, const float* decay, co
     const dim3 sgrid((dim * vdim + 127) / 128, heads, n_entries);
     linear_scan_kernel<<<sgrid, 128, 0, s>>>(heads, dim, vdim, decay, state, ent_first, ent_count, ent_seq, ent_pos0, scratch);
     count_launch();
-    linear_chunk_out_kernel<<<grid, kLinThreads, smem_out, s>>>(heads, dim, vdim, decay, proj, ent_first, ent_count, scratch, o);
+    linear_chunk_out_kernel<<<grid, kLinOutThreads, smem_out, s>>>(heads, dim, vdim, decay, proj, ent_first, ent_count, scratch, o);
     return done();
   }
   const dim3 grid((vdim + kLinCols - 1) / kLinCols, heads, n_entries);
